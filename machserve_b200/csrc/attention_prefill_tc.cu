@@ -56,8 +56,11 @@ __device__ __forceinline__ bool atc_mbar_try(unsigned bar, unsigned parity) {
       : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ bool atc_mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag, int code) {
-  for (int it = 0; it < ATC_WAIT_LIMIT; ++it) {
+// Waits for the phase with the given parity to complete, at most `limit` polls.  Returns false when it gave
+// up (then the block's abort flag and the device's error word are set) or when another thread of the block has.
+__device__ __forceinline__ bool atc_mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag, int code,
+                                              int limit = ATC_WAIT_LIMIT) {
+  for (int it = 0; it < limit; ++it) {
     if (atc_mbar_try(bar, parity)) return true;
     if (*abort_flag) return false;
     if (it > 256) __nanosleep(40);
@@ -568,6 +571,26 @@ MS_API void ms_atc_times(long long* out) { cudaMemcpyFromSymbol(out, g_atc_times
 MS_API void ms_atc_times2(long long* out) { cudaMemcpyFromSymbol(out, g_atc_times2, sizeof(long long) * 64 * 8); }
 MS_API void ms_atc_blocks(unsigned long long* out) { cudaMemcpyFromSymbol(out, g_atc_blocks, sizeof(unsigned long long) * 4096 * 4); }
 #endif
+
+// A wait that runs out, in the form that cannot hang: one thread waits `polls` polls on a barrier in its own
+// shared memory that nothing arrives on, through the helper that every wait of the kernel above uses; no
+// copy and no tensor memory is involved.  Leaves code 19 for ms_attention_tc_status.
+__global__ void atc_wait_probe_kernel(int polls) {
+  __shared__ unsigned long long bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    atc_mbar_init(atc_smem(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    atc_mbar_wait(atc_smem(&bar), 0, &abort_flag, 19, polls);
+  }
+}
+MS_API int ms_attention_tc_wait_probe(int polls, cudaStream_t stream) {
+  MS_REQUIRE(polls >= 1 && polls <= 100000, "attention_tc_wait_probe: 1 to 100000 polls");
+  atc_wait_probe_kernel<<<1, 32, 0, stream>>>(polls);
+  MS_LAUNCH_CHECK("attention_tc_wait_probe");
+  return 0;
+}
 
 MS_API int ms_attention_prefill_tc_supports(int hd, int page_size) {
   return (hd == 64 || hd == 128) && page_size >= 8 && (page_size & (page_size - 1)) == 0;

@@ -52,8 +52,9 @@ __device__ __forceinline__ bool tc_mbar_try(unsigned bar, unsigned parity) {
 }
 // Waits for the phase with the given parity to complete, at most TC_WAIT_LIMIT polls.  Returns false when it
 // gave up or when another thread of the block already has.
-__device__ __forceinline__ bool tc_mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag, int code) {
-  for (int it = 0; it < TC_WAIT_LIMIT; ++it) {
+__device__ __forceinline__ bool tc_mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag, int code,
+                                             int limit = TC_WAIT_LIMIT) {
+  for (int it = 0; it < limit; ++it) {
     if (tc_mbar_try(bar, parity)) return true;
     if (*abort_flag) return false;
     if (it > 256) __nanosleep(40);
@@ -326,6 +327,26 @@ MS_API int ms_gemm_tc_status(int reset) {
     cudaMemcpyToSymbol(g_tc_error, &z, sizeof(int));
   }
   return v;
+}
+
+// A wait that runs out, in the form that cannot hang: one thread waits `polls` polls on a barrier in its own
+// shared memory that nothing arrives on, through the helper that every wait of the kernels here uses; no
+// copy and no tensor memory is involved.  Leaves code 9 for ms_gemm_tc_status.
+__global__ void tc_wait_probe_kernel(int polls) {
+  __shared__ unsigned long long bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    tc_mbar_init(tc_smem(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    tc_mbar_wait(tc_smem(&bar), 0, &abort_flag, 9, polls);
+  }
+}
+MS_API int ms_gemm_tc_wait_probe(int polls, cudaStream_t stream) {
+  MS_REQUIRE(polls >= 1 && polls <= 100000, "gemm_tc_wait_probe: 1 to 100000 polls");
+  tc_wait_probe_kernel<<<1, 32, 0, stream>>>(polls);
+  MS_LAUNCH_CHECK("gemm_tc_wait_probe");
+  return 0;
 }
 
 // out[M, N] = x[M, K] . w[N, K]^T; x, w bfloat16 (row strides ldx, K); out bfloat16 or float32.

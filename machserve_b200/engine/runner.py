@@ -26,7 +26,7 @@ from .. import ops
 from ..cache import CacheManager, OutOfPages
 from ..config import ModelConfig, load_config
 from ..parts import DecoderModel, FixedState, PagedBinding, PagedKV, Runtime, StateBinding, StepContext, Workspace
-from ..weights import load_weights, random_tensors
+from ..weights import load_weights, random_tensors, random_tensors_on_device
 
 _DTYPES = {
     "bfloat16": torch.bfloat16,
@@ -135,9 +135,15 @@ class ModelRunner:
         return cls(config, tensors, dtype=dtype, **kw)
 
     @classmethod
-    def from_random(cls, config: ModelConfig, seed: int, dtype=torch.bfloat16, **kw) -> "ModelRunner":
+    def from_random(cls, config: ModelConfig, seed: int, dtype=torch.bfloat16, on_device: bool = False, **kw) -> "ModelRunner":
+        """Random weights in memory.  By default the values are those of `write_random_model` for the same seed
+        (made on the host, reproducible anywhere); with `on_device` they are drawn by the device's generator,
+        which takes seconds for billions of parameters and is what a benchmark wants."""
         model = DecoderModel(config.model_spec())
         dt = parse_dtype(dtype)
+        if on_device:
+            device = torch.device(kw.get("device", "cuda:0"))
+            return cls(config, random_tensors_on_device(model.tensors(), seed, dt, device), dtype=dt, **kw)
         return cls(config, random_tensors(model.tensors(), seed, dt), dtype=dt, **kw)
 
     def _make_bindings(self):
@@ -435,9 +441,10 @@ class ModelRunner:
 
     def check_device_status(self) -> None:
         """Raises if a tensor-core kernel gave up one of its bounded waits since the last check (synchronizes)."""
-        code = ops.gemm_tc_status()
-        if code:
-            raise RuntimeError(f"a tcgen05 kernel gave up a wait (code {code}); the results of recent steps are not valid")
+        gemm, attention = ops.tc_status_codes()
+        if gemm or attention:
+            raise RuntimeError(f"a tcgen05 kernel gave up a wait (product code {gemm}, attention code {attention}); "
+                               "the results of recent steps are not valid")
 
     def release(self, request: Hashable) -> None:
         """The request is finished: its pages and its slot go back."""

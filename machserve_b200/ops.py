@@ -74,6 +74,8 @@ class _Signatures:
     ms_gemm_small_m_scaled = [P, I, P, I, F, P, P, P, I, I, I, I, I, P]
     ms_gemm_tc = [P, I, P, P, I, I, I, I, I, P]
     ms_gemm_tc_silu_mul = [P, I, P, P, I, I, I, I, P]
+    ms_gemm_tc_wait_probe = [I, P]
+    ms_attention_tc_wait_probe = [I, P]
     ms_take_sampled_tokens = [P, P, P, I, I, P]
     ms_apply_logit_offsets = [P, I, I, P, P, P, P]
     ms_sample = [P, I, I, P, P, P, P, P, P, P]
@@ -557,7 +559,23 @@ def gemm_tc_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor
 def gemm_tc_status(reset: bool = True) -> int:
     """0, or which bounded wait of a tcgen05 kernel gave up (products: 1 producer, 2 issuer, 3 epilogue;
     attention: 11 producer, 12-14 and 16 issuer, 15 softmax threads).  Synchronizes."""
-    return int(lib().ms_gemm_tc_status(1 if reset else 0)) or int(lib().ms_attention_tc_status(1 if reset else 0))
+    codes = tc_status_codes(reset)
+    return codes[0] or codes[1]
+
+
+def tc_status_codes(reset: bool = True):
+    """(code of the tcgen05 products, code of the tcgen05 attention): both are read, and cleared with `reset`,
+    whichever of them is set.  Synchronizes."""
+    return int(lib().ms_gemm_tc_status(1 if reset else 0)), int(lib().ms_attention_tc_status(1 if reset else 0))
+
+
+def tc_wait_probe(kernel: str, polls: int = 1000) -> None:
+    """Launches one thread that waits `polls` polls on a barrier nothing arrives on, through the bounded-wait helper
+    of the tcgen05 products (`kernel="gemm"`, leaves code 9) or of the tcgen05 attention (`"attention"`, code 19):
+    the way to see the give-up path run (error word set, kernel returns, context usable) without a hang."""
+    _need(kernel in ("gemm", "attention"), "tc_wait_probe: kernel is 'gemm' or 'attention'")
+    fn = lib().ms_gemm_tc_wait_probe if kernel == "gemm" else lib().ms_attention_tc_wait_probe
+    _check(fn(int(polls), _stream()), "tc_wait_probe")
 
 
 def attention_prefill_tc_supports(head_dim: int, page_size: int) -> bool:

@@ -88,6 +88,42 @@ def random_tensors(
     return out
 
 
+def random_tensors_on_device(
+    declared: Iterable[TensorDecl],
+    seed: int,
+    dtype: torch.dtype,
+    device,
+    weight_std: float = 0.02,
+    bias_std: float = 0.02,
+    norm_std: float = 0.05,
+) -> Dict[str, torch.Tensor]:
+    """The same kinds of values as `random_tensors`, drawn by the device's own generator: for models of
+    billions of parameters whose values need not be reproducible elsewhere (a benchmark's weights).  A tensor's
+    values depend on (seed, its name) and on the device's generator, not on the other tensors."""
+    out: Dict[str, torch.Tensor] = {}
+    gen = torch.Generator(device=device)
+    for d in declared:
+        if d.name in out or not d.random:
+            continue
+        if d.init == "table":
+            out[d.name] = torch.zeros(d.shape, dtype=torch.int32, device=device)
+            continue
+        if d.init == "zeros":
+            out[d.name] = torch.zeros(d.shape, dtype=dtype, device=device)
+            continue
+        gen.manual_seed(int(_name_key(seed, d.name)) & 0x7FFFFFFFFFFFFFFF)
+        if d.init == "matrix":
+            t = torch.randn(d.shape, dtype=dtype, device=device, generator=gen).mul_(weight_std)
+        elif d.init == "bias":
+            t = torch.randn(d.shape, dtype=torch.float32, device=device, generator=gen).mul_(bias_std).to(dtype)
+        elif d.init == "scale":
+            t = torch.randn(d.shape, dtype=torch.float32, device=device, generator=gen).mul_(norm_std).add_(1.0).to(dtype)
+        else:
+            raise ValueError(f"tensor '{d.name}': unknown init '{d.init}'")
+        out[d.name] = t
+    return out
+
+
 def write_random_model(
     config,
     out_dir,

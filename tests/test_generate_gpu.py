@@ -158,8 +158,9 @@ def test_running_ahead_of_the_host_changes_no_token(model_root):
     assert want[1] == (base[: base.index(base[5]) + 1], "stop") and want[2][1] == "length" and len(want[3][0]) == 20
     got, _ = run(True, 64)
     assert got == want
-    tight, _ = run(True, 8)  # 64 tokens of cache for requests that grow to 17, 25, 12 and 46: they take turns
+    tight, preempted = run(True, 8)  # 64 tokens of cache for requests that grow to 17, 25, 12 and 46: they take turns
     assert tight == want
+    assert preempted > 0, "the tight pool was meant to force a preemption"
 
 
 def test_top_logprobs_through_the_entry_point(model_root):
@@ -226,4 +227,18 @@ def test_random_load_running_ahead_equals_step_by_step(model_root, seed):
     want, _ = run(False)
     got, preempted = run(True)
     assert got == want
-    assert any(r == "stop" for _, r in want) or any(r == "length" for _, r in want)
+    assert preempted > 0, "the pool was meant to be too small for the load: nothing was preempted"
+    assert any(r == "stop" for _, r in want) and any(r == "length" for _, r in want)
+    # the greedy requests against the plain implementation (float32 engine: the same tokens)
+    _, w = read_model_dir(d)
+    kept = [j for k, j in enumerate(jobs) if k != 9]
+    checked = 0
+    for (prompt, n, eos, params, _), (tokens, reason) in zip(kept, want):
+        if params.temperature > 0 or checked >= 6:
+            continue
+        plain = greedy_generate(lambda t: forward_logits(w, cfg, t), prompt, n)
+        if eos is not None and eos in plain:
+            plain = plain[: plain.index(eos) + 1]
+        assert tokens == plain and reason == ("stop" if eos is not None and plain[-1] == eos else "length")
+        checked += 1
+    assert checked >= 3
