@@ -29,7 +29,9 @@ PAGE = 64
 # float32 engine against float64: rounding of float32 sums over up to 18,944 terms
 F32_TOL = 3e-5
 # bfloat16 engine (activations, cache and products rounded to 8 bits in both layers) against float64 on the
-# same bfloat16 weights, relative to the largest logit.
+# same bfloat16 weights, relative to the largest logit.  Worst measured on a B200 over all cuttings: 0.034 at the
+# 0.5B widths, 0.034 at the 1.5B widths, 0.023 at the 7B widths (float32: 7e-6, 8e-6, 1e-5).  The attention is
+# peaked on purpose (scores up to +-12), so a score's rounding of 2^-9 moves a probability by up to 3 %.
 BF16_TOL = 4e-2
 
 SIZES = {
@@ -60,7 +62,6 @@ class World:
         from machserve_b200 import ModelRunner
         from machserve_b200.config import config_from_json
         from machserve_b200.parts import DecoderModel
-        from tests.plain.model import bf16_round
 
         self.size, self.dtype, self.raw = size, dtype, _config(size)
         cfg = config_from_json(self.raw)
@@ -83,7 +84,6 @@ class World:
             tensors = {n: t.to(torch.bfloat16) if t.dim() == 2 else t for n, t in tensors.items()}
         self.weights = {n: t.to(torch.float32).numpy().astype(np.float64) for n, t in tensors.items()}
         self.vocab = self.raw["vocab_size"]
-        long = SIZES[size]["long"]
         # the pool holds the longest request and little more: every later cutting runs on pages given back
         self.pool_tokens = 30 * PAGE
         self.runner = ModelRunner(cfg, tensors, dtype=dtype, page_size=PAGE, num_pages=self.pool_tokens // PAGE,
