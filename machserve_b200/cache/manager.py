@@ -3,7 +3,7 @@
 Host-side bookkeeping only; the device arrays that the ids index are made by the
 engine (`CacheManager.groups` says how many pages of which shape).
 
-* Runs of layers with the same need (kv heads, head size, window) form a GROUP.
+* Runs of layers with the same need (the same planes per token, the same window) form a GROUP.
   A group has its own pool of pages and, per request, its own block table: entry
   i is the page that holds positions [i*page_size, (i+1)*page_size), or -1.
   One page id of a group indexes every run's array of that group.
@@ -23,7 +23,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
-from ..parts.base import CacheNeed, FixedState, PagedKV
+from ..parts.base import CacheNeed, FixedState, PagedCache
 from .pool import Pool, PoolError
 
 
@@ -34,7 +34,7 @@ class OutOfPages(RuntimeError):
 @dataclass
 class CacheGroup:
     index: int
-    need: PagedKV
+    need: PagedCache
     runs: List[int]  # entries of the run order that own a cache in this group
     pool: Pool
 
@@ -63,9 +63,9 @@ class CacheManager:
         self.groups: List[CacheGroup] = []
         self.group_of_run: Dict[int, int] = {}
         self.state_runs: Dict[int, FixedState] = {}
-        by_need: Dict[PagedKV, int] = {}
+        by_need: Dict[PagedCache, int] = {}
         for run, need in enumerate(needs):
-            if isinstance(need, PagedKV):
+            if isinstance(need, PagedCache):
                 if need not in by_need:
                     n = (pages_per_group or {}).get(len(self.groups), num_pages)
                     by_need[need] = len(self.groups)

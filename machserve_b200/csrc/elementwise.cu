@@ -232,24 +232,30 @@ MS_API int ms_add_rmsnorm(float* residual, const void* delta, int delta_dtype, c
   return 0;
 }
 
-// residual += delta, for arrangements that add without a norm following.
-template <typename TD>
-__global__ void residual_add_kernel(float* __restrict__ residual, const TD* __restrict__ delta, size_t n) {
+// out[r, c] += bias[c] in float32, rounded to out's type: the bias of a bfloat16 matrix product, whose kernels
+// (this library's and cuBLAS) add none.  out is [rows, n] with row stride ld.
+template <typename T>
+__global__ void add_bias_kernel(T* __restrict__ out, const float* __restrict__ bias, int n, int ld, size_t total) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) residual[i] += ms_to_float(delta[i]);
+  if (i >= total) return;
+  const size_t r = i / n;
+  const int c = (int)(i - r * n);
+  T* p = out + r * ld + c;
+  *p = ms_from_float<T>(ms_to_float(*p) + bias[c]);
 }
 
-MS_API int ms_residual_add(float* residual, const void* delta, int delta_dtype, long long n, cudaStream_t stream) {
-  if (n == 0) return 0;
-  MS_REQUIRE(n > 0, "residual_add: bad size %lld", n);
-  const unsigned blocks = (unsigned)((n + 255) / 256);
-  if (delta_dtype == MS_F32)
-    residual_add_kernel<float><<<blocks, 256, 0, stream>>>(residual, (const float*)delta, (size_t)n);
-  else if (delta_dtype == MS_BF16)
-    residual_add_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(residual, (const __nv_bfloat16*)delta, (size_t)n);
+MS_API int ms_add_bias(void* out, int dtype, const float* bias, int rows, int n, int ld, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  MS_REQUIRE(rows > 0 && n > 0 && ld >= n, "add_bias: bad sizes rows=%d n=%d ld=%d", rows, n, ld);
+  const size_t total = (size_t)rows * n;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == MS_F32)
+    add_bias_kernel<float><<<blocks, 256, 0, stream>>>((float*)out, bias, n, ld, total);
+  else if (dtype == MS_BF16)
+    add_bias_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)out, bias, n, ld, total);
   else
-    MS_REQUIRE(false, "residual_add: unknown dtype %d", delta_dtype);
-  MS_LAUNCH_CHECK("residual_add");
+    MS_REQUIRE(false, "add_bias: unknown dtype %d", dtype);
+  MS_LAUNCH_CHECK("add_bias");
   return 0;
 }
 

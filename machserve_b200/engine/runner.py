@@ -25,7 +25,8 @@ import torch
 from .. import ops
 from ..cache import CacheManager, OutOfPages
 from ..config import ModelConfig, load_config
-from ..parts import DecoderModel, FixedState, PagedBinding, PagedKV, Runtime, StateBinding, StepContext, Workspace
+from ..parts import DecoderModel, FixedState, PagedBinding, Runtime, StateBinding, StepContext, Workspace
+from ..parts.base import StepShape, Work
 from ..weights import load_weights, random_tensors, random_tensors_on_device
 
 _DTYPES = {
@@ -98,24 +99,44 @@ class ModelRunner:
         self.cache = CacheManager(self.model.cache_needs(), page_size, num_pages, max_requests)
         self.max_pages = (self.max_seq_len + page_size - 1) // page_size
         # device side of the cache: pages per group, block tables per group, state per run
-        self.pages: List[torch.Tensor] = []
+        # (pages[group][plane] : [runs, num_pages, heads, page_size, width])
+        self.pages: List[Dict[str, torch.Tensor]] = []
         self.tables: List[torch.Tensor] = []
         for g in self.cache.groups:
-            shape = (len(g.runs), 2, g.pool.size, g.need.num_kv_heads, page_size, g.need.head_dim)
-            self.pages.append(torch.zeros(shape, dtype=self.dtype, device=self.device))
+            self.pages.append({
+                pl.name: torch.zeros((len(g.runs), g.pool.size, pl.heads, page_size, pl.width), dtype=self.dtype, device=self.device)
+                for pl in g.need.planes
+            })
             self.tables.append(torch.full((max_requests, self.max_pages), -1, dtype=torch.int32, device=self.device))
         self.states: Dict[int, torch.Tensor] = {
             run: torch.zeros((max_requests, *need.shape), dtype=torch.float32, device=self.device)
             for run, need in self.cache.state_runs.items()
         }
         self.bindings = self._make_bindings()
-        # staging for one step's index arrays: pinned host buffers in a ring, one device buffer
-        self._stage_len = 7 * max_step_tokens + 10 * max_requests + 4 * (max_step_tokens // 64) + 16
+        # the parts that want work lists of their own staged with a step (one per key)
+        self._planners: Dict[Hashable, object] = {}
+        for part in self.model.parts():
+            key = part.plan_key()
+            if key is not None and key not in self._planners:
+                self._planners[key] = part
+        # staging for one step's index arrays: pinned host buffers in a ring, one device buffer.  A decoding step
+        # is padded to a power of two of rows, which may exceed max_requests.
+        pad = 1
+        while pad < max_requests:
+            pad *= 2
+        rows, seqs = max(max_step_tokens, pad), pad
+        self._stage_len = 6 * rows + 4 * seqs + 1 + sum(p.plan_words(rows, seqs) for p in self._planners.values()) + 16
         self._pinned = [torch.empty(self._stage_len, dtype=torch.int32).pin_memory() for _ in range(3)]
         self._pinned_events: List[Optional[torch.cuda.Event]] = [None] * len(self._pinned)
         self._turn = 0
         self._device_stage = torch.empty(self._stage_len, dtype=torch.int32, device=self.device)
-        self._row_stage = torch.empty((max_requests, self.max_pages), dtype=torch.int32).pin_memory()
+        # changed block-table rows go the same way: per group a region of slots and rows in a pinned ring
+        self._row_words = 1 + self.max_pages
+        region = max_requests * self._row_words
+        self._row_pinned = [torch.empty(max(1, len(self.cache.groups)) * region, dtype=torch.int32).pin_memory() for _ in range(3)]
+        self._row_events: List[Optional[torch.cuda.Event]] = [None] * len(self._row_pinned)
+        self._row_turn = 0
+        self._row_device = torch.empty(max(1, len(self.cache.groups)) * region, dtype=torch.int32, device=self.device)
         self.steps = 0
         self._sampled: Optional[torch.Tensor] = None
         self.h2d_bytes = 0  # bytes of index arrays and block-table rows copied to the device so far
@@ -124,6 +145,7 @@ class ModelRunner:
         self._graphs: Dict[Tuple[int, int], Tuple[torch.cuda.CUDAGraph, torch.Tensor, int]] = {}
         self._shape_graphs: Dict[tuple, Tuple[torch.cuda.CUDAGraph, torch.Tensor, int]] = {}
         self._shape_seen: Dict[tuple, int] = {}
+        self._decode_plan_cache: Dict[Tuple[int, int], tuple] = {}
 
     # ---------------------------------------------------------------- builders
 
@@ -153,7 +175,7 @@ class ModelRunner:
             if owner in self.cache.group_of_run:
                 g = self.cache.group_of_run[owner]
                 j = self.cache.groups[g].runs.index(owner)
-                out.append(PagedBinding(g, self.pages[g][j, 0], self.pages[g][j, 1], self.cache.groups[g].need.window))
+                out.append(PagedBinding(g, {name: arr[j] for name, arr in self.pages[g].items()}, self.cache.groups[g].need.window))
             elif owner in self.states:
                 out.append(StateBinding(self.states[owner]))
             else:
@@ -216,35 +238,58 @@ class ModelRunner:
             raise
 
     def _upload_tables(self) -> None:
+        """Block-table rows that changed go to the device: staged in pinned memory (a ring guarded by events, so the
+        host never waits for the device here), copied without blocking, and scattered to their slots."""
         dirty = self.cache.take_dirty()
         if not dirty:
             return
-        for g in range(len(self.cache.groups)):
-            rows = [r for (r, gg) in dirty if gg == g and r in self.cache.requests]
-            if not rows:
-                continue
-            slots = []
+        by_group: Dict[int, list] = {}
+        for (r, g) in dirty:
+            if r in self.cache.requests:
+                by_group.setdefault(g, []).append(r)
+        if not by_group:
+            return
+        turn = self._row_turn
+        self._row_turn = (turn + 1) % len(self._row_pinned)
+        if self._row_events[turn] is not None:
+            self._row_events[turn].synchronize()
+        host = self._row_pinned[turn].numpy()
+        words, region = self._row_words, self.max_requests * self._row_words
+        for g, rows in by_group.items():
+            n = len(rows)  # the region of group g: n slots, then n rows
+            at = g * region
+            slots = host[at : at + n]
+            rec = host[at + n : at + n * words].reshape(n, self.max_pages)
+            rec[:] = -1
             for i, r in enumerate(rows):
                 table = self.cache.block_table(r, g)
-                row = self._row_stage[i]
-                row.fill_(-1)
-                row[: len(table)] = torch.tensor(table, dtype=torch.int32)
-                slots.append(self.cache.state_slot(r))
-            idx = torch.tensor(slots, dtype=torch.int64, device=self.device)
-            self.h2d_bytes += len(rows) * (self.max_pages * 4 + 8)
-            self.tables[g].index_copy_(0, idx, self._row_stage[: len(rows)].to(self.device))
+                slots[i] = self.cache.state_slot(r)
+                rec[i, : len(table)] = table
+            dev = self._row_device[at : at + n * words]
+            dev.copy_(self._row_pinned[turn][at : at + n * words], non_blocking=True)
+            self.tables[g].index_copy_(0, dev[:n], dev[n:].view(n, self.max_pages))
+            self.h2d_bytes += 4 * n * words
+        ev = torch.cuda.Event()
+        ev.record()
+        self._row_events[turn] = ev
 
     @staticmethod
-    def _layout(T: int, S: int, W: int, n_single: int, n_tiles: int, n_big: int = 0):
-        """Where each index array of a step lies in the staging buffer: name -> (offset, length)."""
+    def _layout(T: int, S: int, W: int, plan_sizes=()):
+        """Where each index array of a step lies in the staging buffer: name -> (offset, length).  The parts'
+        work lists follow the step's own arrays under the names (key, list name)."""
         views, o = {}, 0
         for name, n in (("token_ids", T), ("from_sampled", T), ("positions", T), ("seq_of_token", T), ("slot_of_token", T),
                         ("cu_tokens", S + 1), ("seq_start", S), ("seq_len", S), ("state_slots", S),
-                        ("want_rows", W), ("single_rows", n_single), ("tile_row0", n_tiles), ("tile_rows", n_tiles),
-                        ("big_tile_row0", n_big), ("big_tile_rows", n_big)):
+                        ("want_rows", W), *plan_sizes):
             views[name] = (o, n)
             o += n
         return views, o
+
+    def _plans(self, shape: StepShape):
+        """Every planner's lists for this step: [(key, WorkPlan)], and their lengths as _layout wants them."""
+        plans = [(key, part.plan(shape)) for key, part in self._planners.items()]
+        sizes = [((key, name), len(lst)) for key, plan in plans for name, lst in plan.lists.items()]
+        return plans, sizes
 
     def _pinned_turn(self):
         turn = self._turn
@@ -265,17 +310,20 @@ class ModelRunner:
             (a, n), (b, _) = views["token_ids"], views["from_sampled"]
             ops.take_sampled_tokens(self._device_stage[a : a + n], self._device_stage[b : b + n], self._sampled)
 
-    def _context(self, views, T, S, W, n_single, n_tiles, max_q, max_len, cu=(), start=(), slots=(), n_big=0) -> StepContext:
+    def _context(self, views, T, S, W, plans, max_q, max_len, cu=(), start=(), slots=()) -> StepContext:
         dev = self._device_stage
         d = {name: dev[a : a + n] for name, (a, n) in views.items()}
+        work = {
+            key: Work({name: d[(key, name)] for name in plan.lists}, {name: len(lst) for name, lst in plan.lists.items()},
+                      tuple(plan.shape))
+            for key, plan in plans
+        }
         return StepContext(
             rt=self.rt, num_tokens=T, num_seqs=S, token_ids=d["token_ids"], positions=d["positions"],
             seq_of_token=d["seq_of_token"], slot_of_token=d["slot_of_token"], cu_tokens=d["cu_tokens"],
             seq_start=d["seq_start"], seq_len=d["seq_len"], state_slots=d["state_slots"],
             block_tables={g: self.tables[g] for g in range(len(self.tables))},
-            want_rows=d["want_rows"], num_wanted=W, single_rows=d["single_rows"], num_single=n_single,
-            tile_row0=d["tile_row0"], tile_rows=d["tile_rows"], num_tiles=n_tiles,
-            big_tile_row0=d["big_tile_row0"], big_tile_rows=d["big_tile_rows"], num_big_tiles=n_big,
+            want_rows=d["want_rows"], num_wanted=W, work=work,
             host_cu_tokens=[int(x) for x in cu], host_seq_start=[int(x) for x in start],
             host_state_slots=[int(x) for x in slots], max_query_len=max_q, max_seq_len=max_len,
             decode_only=max_q == 1,
@@ -285,24 +333,23 @@ class ModelRunner:
         """Fills one pinned buffer with the step's index arrays and copies it to the device in one transfer."""
         turn = self._pinned_turn()
         host = self._pinned[turn].numpy()
-        T = sum(len(e.tokens) for e in entries)
-        S = len(entries)
+        counts = [len(e.tokens) for e in entries]
+        starts = [self.cache.num_tokens(e.request) for e in entries]
+        T, S = sum(counts), len(entries)
         W = sum(len(e.want) for e in entries)
-        n_single = sum(1 for e in entries if len(e.tokens) == 1)
-        n_tiles = sum((len(e.tokens) + 63) // 64 for e in entries if len(e.tokens) > 1)
-        n_big = sum((len(e.tokens) + 127) // 128 for e in entries if len(e.tokens) > 1)
-        views, total = self._layout(T, S, W, n_single, n_tiles, n_big)
+        row0, row = [], 0
+        for n in counts:
+            row0.append(row)
+            row += n
+        plans, plan_sizes = self._plans(StepShape(T, S, row0, counts, starts))
+        views, total = self._layout(T, S, W, plan_sizes)
         h = {name: host[a : a + n] for name, (a, n) in views.items()}
-        big0, bign, bi = h["big_tile_row0"], h["big_tile_rows"], 0
         tok, pos, seq, slot = h["token_ids"], h["positions"], h["seq_of_token"], h["slot_of_token"]
         cu, start, length, slots, want = h["cu_tokens"], h["seq_start"], h["seq_len"], h["state_slots"], h["want_rows"]
-        single, tile0, tilen = h["single_rows"], h["tile_row0"], h["tile_rows"]
-        si = ti = row = w = 0
+        w = 0
         cu[0] = 0
-        max_q = max_len = 0
         for i, e in enumerate(entries):
-            n = len(e.tokens)
-            p0 = self.cache.num_tokens(e.request)
+            n, p0, row = counts[i], starts[i], row0[i]
             s = self.cache.state_slot(e.request)
             tok[row : row + n] = e.tokens
             h["from_sampled"][row : row + n] = -1 if e.from_sampled is None else e.from_sampled
@@ -313,21 +360,14 @@ class ModelRunner:
             for k in e.want:
                 want[w] = row + int(k)
                 w += 1
-            if n == 1:
-                single[si] = row
-                si += 1
-            else:
-                for a in range(0, n, 64):
-                    tile0[ti], tilen[ti] = row + a, min(64, n - a)
-                    ti += 1
-                for a in range(0, n, 128):
-                    big0[bi], bign[bi] = row + a, min(128, n - a)
-                    bi += 1
-            row += n
-            cu[i + 1] = row
-            max_q, max_len = max(max_q, n), max(max_len, p0 + n)
+            cu[i + 1] = row + n
+        for key, plan in plans:
+            for name, lst in plan.lists.items():
+                h[(key, name)][:] = lst
         self._send(turn, total, views, entries)
-        return self._context(views, T, S, W, n_single, n_tiles, max_q, max_len, cu, start, slots, n_big)
+        max_q = max(counts)
+        max_len = max(p + n for p, n in zip(starts, counts))
+        return self._context(views, T, S, W, plans, max_q, max_len, cu, start, slots)
 
     # ------------------------------------------------------- decoding with graphs
 
@@ -341,12 +381,24 @@ class ModelRunner:
         longest = max(self.cache.num_tokens(e.request) for e in entries) + 1
         return b, -(-longest // 512) * 512
 
-    def _stage_decode(self, entries: Sequence[StepEntry], b: int):
+    def _decode_plans(self, b: int, length: int):
+        """The parts' plans for a decoding step of `b` rows (padding included) whose longest context is `length`:
+        they depend on nothing else, so they are made once per graph."""
+        key = (b, length)
+        hit = self._decode_plan_cache.get(key)
+        if hit is None:
+            plans, sizes = self._plans(StepShape(b, b, list(range(b)), [1] * b, [length - 1] * b))
+            arrays = [((k, name), np.asarray(lst, dtype=np.int32)) for k, plan in plans for name, lst in plan.lists.items()]
+            hit = self._decode_plan_cache[key] = (plans, sizes, arrays)
+        return hit
+
+    def _stage_decode(self, entries: Sequence[StepEntry], b: int, length: int):
         """The staging of a decoding step padded to `b` rows: padding rows belong to no request."""
         turn = self._pinned_turn()
         host = self._pinned[turn].numpy()
         s = len(entries)
-        views, total = self._layout(b, b, b, b, 0)
+        plans, plan_sizes, arrays = self._decode_plans(b, length)
+        views, total = self._layout(b, b, b, plan_sizes)
         h = {name: host[a : a + n] for name, (a, n) in views.items()}
         p0 = [self.cache.num_tokens(e.request) for e in entries]
         sl = [self.cache.state_slot(e.request) for e in entries]
@@ -359,15 +411,16 @@ class ModelRunner:
             h[name][s:] = pad
         h["cu_tokens"][:] = np.arange(b + 1, dtype=np.int32)
         h["want_rows"][:] = np.arange(b, dtype=np.int32)
-        h["single_rows"][:] = np.arange(b, dtype=np.int32)
+        for name, arr in arrays:
+            h[name][:] = arr
         self._send(turn, total, views, entries)
-        return views
+        return views, plans
 
     def _decode_with_graph(self, entries: Sequence[StepEntry], b: int, length: int) -> torch.Tensor:
-        views = self._stage_decode(entries, b)
+        views, plans = self._stage_decode(entries, b, length)
         key = (b, length)
         if key not in self._graphs:
-            ctx = self._context(views, b, b, b, b, 0, 1, length)
+            ctx = self._context(views, b, b, b, plans, 1, length)
             self.model.forward(ctx, self.bindings)  # sizes the scratch memory and loads every kernel
             torch.cuda.current_stream().synchronize()
             before = ops.launches()
@@ -415,8 +468,8 @@ class ModelRunner:
         ctx = self._stage(entries)
         if not self.use_graphs:
             return self.model.forward(ctx, self.bindings)
-        key = (ctx.num_tokens, ctx.num_seqs, ctx.num_wanted, ctx.num_single, ctx.num_tiles, ctx.num_big_tiles,
-               -(-ctx.max_seq_len // 512) if ctx.num_single else 0)
+        key = (ctx.num_tokens, ctx.num_seqs, ctx.num_wanted,
+               tuple((k, tuple(w.sizes.values()), w.shape) for k, w in ctx.work.items()))
         hit = self._shape_graphs.get(key)
         if hit is not None:
             graph, logits, launches = hit
@@ -456,7 +509,7 @@ class ModelRunner:
 
     def memory_plan(self) -> Dict[str, int]:
         weights = sum(t.numel() * t.element_size() for t in _unique_tensors(self.model))
-        pages = sum(p.numel() * p.element_size() for p in self.pages)
+        pages = sum(p.numel() * p.element_size() for planes in self.pages for p in planes.values())
         return {"weights_bytes": weights, "cache_bytes": pages, "workspace_bytes": self.rt.workspace.nbytes()}
 
 

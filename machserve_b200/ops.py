@@ -58,7 +58,7 @@ class _Signatures:
     P, I, F, LL = c_void_p, c_int, c_float, c_longlong
     ms_embed_gather = [P, I, P, P, I, I, I, P]
     ms_add_rmsnorm = [P, P, I, P, P, I, P, I, I, F, P]
-    ms_residual_add = [P, P, I, LL, P]
+    ms_add_bias = [P, I, P, I, I, I, P]
     ms_silu_mul = [P, P, I, I, I, P]
     ms_rope_kv_store = [P, I, I, P, P, P, P, I, I, P, I, I, P, P, P, I, I, I, I, I, I, P]
     ms_attention_generic = [P, P, P, P, I, I, P, P, P, I, I, I, I, I, I, I, I, F, P]
@@ -192,11 +192,12 @@ def add_rmsnorm(
     return out
 
 
-def residual_add(residual: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
-    _need(residual.dtype == torch.float32 and residual.is_contiguous() and delta.is_contiguous(), "residual_add: bad layout")
-    _need(delta.numel() >= residual.numel(), "residual_add: delta is smaller than the residual")
-    _check(lib().ms_residual_add(_ptr(residual), _ptr(delta), _code(delta), residual.numel(), _stream()), "residual_add")
-    return residual
+def add_bias(out: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """out[r, c] += bias[c]: out [rows, n] float32 or bfloat16 (unit column stride), bias float32 [n]."""
+    rows, n = out.shape
+    _need(out.stride(1) == 1 and bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == n, "add_bias: bad arguments")
+    _check(lib().ms_add_bias(_ptr(out), _code(out), _ptr(bias), rows, n, out.stride(0), _stream()), "add_bias")
+    return out
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
@@ -607,21 +608,21 @@ def attention_prefill_tc(q, k_pages, v_pages, out, tile_row0, tile_rows, num_til
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
-    """out = x . w^T (+ bias).  float32 goes to the CUDA-core kernel.  bfloat16 with few rows
+    """out = x . w^T (+ bias, float32 [n]).  float32 goes to the CUDA-core kernel.  bfloat16 with few rows
     (decoding) goes to the weight-streaming tensor-core kernel; with many rows it goes to the
     library matrix product (cuBLAS through torch), where the reference too calls its library
-    (hipBLAS GemmEx, crates/mach-model/src/kernels.rs:6416-6455 of gqf2008/machserve)."""
+    (hipBLAS GemmEx, crates/mach-model/src/kernels.rs:6416-6455 of gqf2008/machserve); a bias is then
+    added by a kernel of its own (the built-in attention adds its bias inside its rotary kernel instead)."""
     if x.dtype == torch.float32:
         return gemm_f32(x, w, bias, out)
     _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "linear: operands must both be bfloat16 or float32")
-    _need(bias is None, "linear: the bfloat16 product takes no bias (it is added by the kernel that follows)")
     if gemm_small_m_preferred(x.shape[0], w.shape[0], x.shape[1]) and x.stride(0) % 8 == 0:
-        return gemm_small_m(x, w, out)
-    if out.dtype == torch.bfloat16:
+        gemm_small_m(x, w, out)
+    elif out.dtype == torch.bfloat16:
         torch.mm(x, w.t(), out=out)
     else:
         torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
-    return out
+    return add_bias(out, bias) if bias is not None else out
 
 
 def apply_logit_offsets(logits, row_ptr, tokens, amounts):

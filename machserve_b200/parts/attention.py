@@ -5,7 +5,7 @@ import torch
 
 from .. import ops
 from ..weights.loader import TensorDecl
-from .base import POSITION_ENCODINGS, Mixer, PagedKV, matrix, register_mixer, vector_f32
+from .base import POSITION_ENCODINGS, Mixer, PagedKV, RowStats, WorkPlan, as_delta, matrix, register_mixer, vector_f32
 
 
 @register_mixer("attention")
@@ -27,6 +27,9 @@ class Attention(Mixer):
     """
 
     graph_safe = True  # unless its position encoding is not (see bind)
+    PLAN = "attention"  # the key of its work lists: every attention layer of a model shares them
+    TILE, BIG_TILE = 64, 128  # rows of a prompt portion that one block of the mma.sync / tcgen05 kernel attends
+    CONTEXT_BUCKET = 512  # a decoding step's launch shape is chosen from its longest context rounded up to this
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -97,6 +100,66 @@ class Attention(Mixer):
         self.tc_prefill = self.fast and self.hd in (64, 128)
         self.tc_pages = {p for p in (8, 16, 32, 64, 128, 256, 512, 1024) if ops.attention_prefill_tc_supports(self.hd, p)}
 
+    # -- work lists: the rows sorted by how they are attended --------------------------------------------------
+
+    def plan_key(self):
+        return self.PLAN
+
+    def plan_words(self, max_rows, max_seqs):
+        return max_seqs + 2 * (max_rows // self.TILE + max_seqs) + 2 * (max_rows // self.BIG_TILE + max_seqs)
+
+    def plan(self, step):
+        """Rows that are alone in their sequence (decoding) go to the kernel that splits a row's keys over blocks;
+        portions of prompts are cut into tiles of up to 64 and up to 128 consecutive rows for the two prompt kernels."""
+        single, t0, tn, b0, bn = [], [], [], [], []
+        longest = 0
+        for row, n, start in zip(step.row0, step.count, step.start):
+            if n == 1:
+                single.append(row)
+                longest = max(longest, start + 1)
+            else:
+                for a in range(0, n, self.TILE):
+                    t0.append(row + a)
+                    tn.append(min(self.TILE, n - a))
+                for a in range(0, n, self.BIG_TILE):
+                    b0.append(row + a)
+                    bn.append(min(self.BIG_TILE, n - a))
+        lists = {"single_rows": single, "tile_row0": t0, "tile_rows": tn, "big_tile_row0": b0, "big_tile_rows": bn}
+        return WorkPlan(lists, (-(-longest // self.CONTEXT_BUCKET),))
+
+    # -- with few rows in bfloat16: the norm in front and the add behind inside the products -------------------------
+    fused_rows = 16
+
+    def fuse_norm(self, norm):
+        rt = self.rt
+        ok = (rt.dtype == torch.bfloat16 and (self.position is None or self.table is not None)
+              and self.hidden % 8 == 0 and self.qw % 8 == 0
+              # matrices that the small-row products stream faster than the library does (up to about 64 MB)
+              and all(w.numel() * w.element_size() <= ops.SMALL_M_MAX_WEIGHT_BYTES for w in (self.w_qkv, self.w_o)))
+        return ok and norm.fold_into(self.w_qkv)
+
+    def forward_fused(self, ctx, residual, pending, norm, cache=None, owns_cache=True):
+        """The QKV product reads the residual's bfloat16 copy and divides its output rows by the rows' rms; the
+        output product adds into the float32 residual and leaves the rows' sums of squares and a bfloat16 copy."""
+        rt, ws = self.rt, self.rt.workspace
+        t, d = residual.shape
+        nb = ops.gemm_small_m_stats_blocks(d)
+        store = owns_cache and self.has_kv
+        width = self.qkv_width(store)
+        qkv = ws.get("attn.qkv", (t, width), rt.dtype)
+        if isinstance(pending, RowStats) and pending.copy is not None:
+            ops.gemm_small_m_scaled(pending.copy, pending.stats, pending.blocks, norm.eps, self.w_qkv[:width], None, qkv)
+        else:  # the first block after the embedding, or after a part that returned a delta
+            xn = ws.get("block.normed", (t, d), rt.dtype)
+            norm.forward(residual, as_delta(pending), xn)
+            ops.linear(xn, self.w_qkv[:width], None, qkv)
+        attended = ws.get("attn.out", (t, self.qw), rt.dtype)
+        self.encode_attend(ctx, qkv, cache, store, attended)
+        stats = ws.get("block.stats_mixer", (t, nb), torch.float32)
+        xcopy = ws.get("block.residual_copy", (t, d), rt.dtype)
+        ops.gemm_small_m_resadd(attended, self.w_o, residual, stats, xcopy)
+        return RowStats(stats, nb, xcopy)
+
     def forward(self, ctx, x, cache, owns_cache=True):
         rt, t = self.rt, x.shape[0]
         ws = rt.workspace
@@ -135,15 +198,18 @@ class Attention(Mixer):
 
     def encode_attend(self, ctx, qkv, cache, store: bool, out):
         """encode_store and attend; one kernel when every row is alone in its sequence (a decoding step)."""
-        if self.fuse_encode and ctx.num_single == qkv.shape[0] and ctx.num_tiles == 0 and qkv.stride(0) % 8 == 0:
+        work = ctx.work[self.PLAN]
+        if (self.fuse_encode and work.sizes["single_rows"] == qkv.shape[0] and work.sizes["tile_row0"] == 0
+                and qkv.stride(0) % 8 == 0):
             return self._attend_single(ctx, None, cache, out, raw=(qkv, store))
         return self.attend(ctx, self.encode_store(ctx, qkv, cache, store), cache, out)
 
     def _attend_single(self, ctx, q, cache, out, raw=None):
         """Rows that are alone in their sequences: a cluster of blocks per (row, kv head)."""
-        rt, t = self.rt, ctx.num_single
+        work = ctx.work[self.PLAN]
+        rt, t = self.rt, work.sizes["single_rows"]
         table = cache.block_table(ctx)
-        tiles = (ctx.max_seq_len + 63) // 64
+        tiles = (work.shape[0] * self.CONTEXT_BUCKET + 63) // 64  # of the longest decoding context, by bucket
         if self.window:
             tiles = min(tiles, (self.window + 63) // 64 + 1)
         # about two blocks for every SM, never more blocks than tiles
@@ -165,7 +231,7 @@ class Attention(Mixer):
         return ops.attention_decode_cluster(
             q, cache.k_pages, cache.v_pages, out, ctx.positions, ctx.slot_of_token, table, self.hq, self.hkv,
             self.hd, self.window, self.scale, splits, stages,
-            rows=None if ctx.num_tiles == 0 and t == q.shape[0] else ctx.single_rows, num_rows=t, warps=warps,
+            rows=None if work.sizes["tile_row0"] == 0 and t == q.shape[0] else work.lists["single_rows"], num_rows=t, warps=warps,
         )
 
     def attend(self, ctx, q, cache, out):
@@ -180,17 +246,19 @@ class Attention(Mixer):
                 self.hq, self.hkv, self.hd, self.window, self.scale,
             )
         table = cache.block_table(ctx)
-        if ctx.num_single:
+        work = ctx.work[self.PLAN]
+        lists, sizes = work.lists, work.sizes
+        if sizes["single_rows"]:
             self._attend_single(ctx, q, cache, out)
-        if ctx.num_big_tiles and self.tc_prefill and cache.k_pages.shape[2] in self.tc_pages:
+        if sizes["big_tile_row0"] and self.tc_prefill and cache.k_pages.shape[2] in self.tc_pages:
             # portions of prompts on the tcgen05 tensor cores, in tiles of up to 128 rows
             ops.attention_prefill_tc(
-                q, cache.k_pages, cache.v_pages, out, ctx.big_tile_row0, ctx.big_tile_rows, ctx.num_big_tiles,
+                q, cache.k_pages, cache.v_pages, out, lists["big_tile_row0"], lists["big_tile_rows"], sizes["big_tile_row0"],
                 ctx.positions, ctx.slot_of_token, table, self.hq, self.hkv, self.hd, self.window, self.scale,
             )
-        elif ctx.num_tiles:
+        elif sizes["tile_row0"]:
             ops.attention_prefill(
-                q, cache.k_pages, cache.v_pages, out, ctx.tile_row0, ctx.tile_rows, ctx.num_tiles, ctx.positions,
+                q, cache.k_pages, cache.v_pages, out, lists["tile_row0"], lists["tile_rows"], sizes["tile_row0"], ctx.positions,
                 ctx.slot_of_token, table, self.hq, self.hkv, self.hd, self.window, self.scale,
             )
         return out

@@ -13,14 +13,19 @@ What every part does:
   its kernels read;
 * `forward(...)` runs it on the tokens of one step.
 
-A mixer also says what it needs of the cache (`cache_need()`): pages of keys and
-values (`PagedKV`, all keys or a window of them), a fixed-size state per request
-(`FixedState`), or nothing.
+A mixer also says what it needs of the cache (`cache_need()`): pages of one or more
+planes per token (`PagedCache`; keys and values are two equal planes, `PagedKV`; all
+tokens or a window of them), a fixed-size state per request (`FixedState`), or nothing.
+
+Two optional protocols let a part join the engine's faster paths without the engine
+knowing its class: `plan_key`/`plan` (host work lists staged with the step's index
+arrays) and `fuse_norm`/`forward_fused` (the norm in front of a part and the add behind
+it done by the part's own kernels).
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
-from typing import Callable, Dict, List, Optional, Tuple, Type, Union
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, Hashable, List, Optional, Sequence, Tuple, Type, Union
 
 import torch
 
@@ -32,12 +37,33 @@ from ..weights.loader import TensorDecl
 
 
 @dataclass(frozen=True)
-class PagedKV:
-    """Keys and values of every token (or of the last `window` tokens) in pages."""
+class CachePlane:
+    """One array of a paged cache: per token `heads` vectors of `width` elements of the runtime's dtype.
+    Its pages on the device are [num_pages, heads, page_size, width]."""
 
-    num_kv_heads: int
-    head_dim: int
+    name: str
+    heads: int
+    width: int
+
+    def elements_per_token(self) -> int:
+        return self.heads * self.width
+
+
+@dataclass(frozen=True)
+class PagedCache:
+    """What a mixer keeps per token, in pages: one or more planes, for every token or for the last `window`
+    tokens.  Runs of layers whose needs are equal share a group of pages and one block table per request."""
+
+    planes: Tuple[CachePlane, ...]
     window: Optional[int] = None
+
+    def elements_per_token(self) -> int:
+        return sum(p.elements_per_token() for p in self.planes)
+
+
+def PagedKV(num_kv_heads: int, head_dim: int, window: Optional[int] = None) -> PagedCache:
+    """Keys and values of every token (or of the last `window` tokens): two equal planes, "k" and "v"."""
+    return PagedCache((CachePlane("k", num_kv_heads, head_dim), CachePlane("v", num_kv_heads, head_dim)), window)
 
 
 @dataclass(frozen=True)
@@ -47,7 +73,7 @@ class FixedState:
     shape: Tuple[int, ...]
 
 
-CacheNeed = Union[PagedKV, FixedState, None]
+CacheNeed = Union[PagedCache, FixedState, None]
 
 
 # --------------------------------------------------------------------- runtime
@@ -111,6 +137,46 @@ class RowStats:
     copy: Optional[torch.Tensor] = None  # the residual rounded to the runtime's dtype, if its producer left one
 
 
+def as_delta(pending):
+    """What a norm adds to the residual before it normalises: a `RowStats` says that the add has been done."""
+    return None if isinstance(pending, RowStats) else pending
+
+
+# ------------------------------------------------------------------- work plans
+
+
+@dataclass
+class StepShape:
+    """The rows of one step as the host knows them: what `Part.plan` makes its work lists from.
+    Sequence i brings rows [row0[i], row0[i] + count[i]) at positions start[i], start[i] + 1, ...
+    A step that is padded to a fixed size ends with sequences of one row that belong to no request."""
+
+    rows: int
+    seqs: int
+    row0: Sequence[int]
+    count: Sequence[int]
+    start: Sequence[int]
+
+
+@dataclass
+class WorkPlan:
+    """Host lists of int32 that a part wants on the device for one step (`lists`, by name), and whatever
+    else its launches depend on beyond the lengths of those lists (`shape`, hashable): a step is captured in
+    a CUDA graph under the lengths and shapes of its plans."""
+
+    lists: Dict[str, Sequence[int]]
+    shape: Tuple = ()
+
+
+@dataclass
+class Work:
+    """A staged plan: the lists as device tensors, their lengths, and the plan's shape."""
+
+    lists: Dict[str, torch.Tensor]
+    sizes: Dict[str, int]
+    shape: Tuple = ()
+
+
 # ------------------------------------------------------------------ interfaces
 
 
@@ -129,6 +195,55 @@ class Part:
     def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         self.rt = rt
 
+    # -- work lists (optional) -------------------------------------------------------------------------
+    # A part whose kernels want lists made on the host (rows sorted by kind, tiles of rows, chunks of a scan)
+    # names a key; parts with equal keys share one plan per step.  The step function calls `plan` once per key,
+    # stages the lists with the step's index arrays in one transfer, and hands them on as `ctx.work[key]`.
+
+    def plan_key(self) -> Optional[Hashable]:
+        return None
+
+    def plan(self, step: StepShape) -> WorkPlan:
+        raise NotImplementedError
+
+    def plan_words(self, max_rows: int, max_seqs: int) -> int:
+        """The most int32 words the lists of one step can have, for steps of up to `max_rows` rows in `max_seqs` sequences."""
+        return 0
+
+    # -- the norm in front and the add behind, inside the part's own kernels (optional) ----------------------
+    # Asked once, when the block is bound: a part that can read the residual's rounded copy and its rows' sums
+    # of squares (`RowStats`) instead of normed rows takes what it needs of `norm` (see `Norm.fold_into`) and
+    # returns True.  `forward_fused` is then used for steps of up to `fused_rows` rows.
+
+    fused_rows = 0
+
+    def fuse_norm(self, norm: "Norm") -> bool:
+        return False
+
+    def forward_fused(self, ctx, residual, pending, norm: "Norm", cache=None, owns_cache: bool = True) -> "RowStats":
+        """residual += part(norm(residual + pending)); `pending` is a delta, None, or the `RowStats` of a part
+        that has already added its delta.  Returns the `RowStats` of the new residual."""
+        raise NotImplementedError
+
+
+class TokenEmbedding(Part):
+    """Token ids to the residual stream: forward(ctx, out) writes the float32 rows out[T, hidden] for `ctx.token_ids`."""
+
+    def forward(self, ctx, out):
+        raise NotImplementedError
+
+
+class Head(Part):
+    """The final hidden rows to logits: forward(ctx, x, out) with x [W, hidden] in the runtime's dtype (the final
+    norm's output for the wanted rows) writes float32 out[W, vocab].  `bind` is also given the model's embedding
+    part, for a head that shares its table."""
+
+    def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime, embedding: Optional[TokenEmbedding] = None) -> None:
+        self.rt = rt
+
+    def forward(self, ctx, x, out):
+        raise NotImplementedError
+
 
 class Norm(Part):
     """y = norm(x).  `forward` takes the float32 residual [T, d] and an optional delta to add first.
@@ -140,6 +255,12 @@ class Norm(Part):
 
     def forward(self, residual, delta, out, rows=None):
         raise NotImplementedError
+
+    def fold_into(self, matrix: torch.Tensor) -> bool:
+        """For a part that fuses this norm (`Part.fuse_norm`): if the norm is y = x / rms(x, eps) * g, multiply the
+        columns of `matrix` [n, size] by g (in float32, rounded once), keep a weight of one from now on, so that
+        every path computes with the same matrix, and return True with `self.eps` set.  Any other norm returns False."""
+        return False
 
 
 class PositionEncoding(Part):
@@ -191,14 +312,22 @@ class Block:
 
     forward(ctx, residual, pending, cache, owns_cache) -> pending: `residual` is
     the float32 stream [T, hidden]; `pending` is a delta not yet added to it
-    (or None); the block returns the delta that the next norm adds.
+    (or None); the block returns the delta that the next norm adds.  A block that
+    sets `accepts_row_stats` may also be given, and may return, a `RowStats` (the
+    delta has been added already); other blocks, and every norm, see None in its place.
     """
+
+    accepts_row_stats = False
 
     def __init__(self, spec: LayerSpec, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, ff_norm: Norm):
         self.spec, self.mixer, self.feed_forward, self.mixer_norm, self.ff_norm = spec, mixer, feed_forward, mixer_norm, ff_norm
 
     def parts(self) -> List[Part]:
         return [self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward]
+
+    def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        for p in self.parts():
+            p.bind(tensors, rt)
 
     def forward(self, ctx, residual, pending, cache, owns_cache=True):
         raise NotImplementedError
@@ -228,12 +357,16 @@ class _Registry:
         return self.items[spec.kind](spec, *args)
 
 
+EMBEDDINGS = _Registry("embedding")
+HEADS = _Registry("head")
 MIXERS = _Registry("mixer")
 FEED_FORWARDS = _Registry("feed-forward")
 NORMS = _Registry("norm")
 POSITION_ENCODINGS = _Registry("position encoding")
 BLOCKS = _Registry("block")
 
+register_embedding = EMBEDDINGS.register
+register_head = HEADS.register
 register_mixer = MIXERS.register
 register_feed_forward = FEED_FORWARDS.register
 register_norm = NORMS.register
@@ -242,8 +375,9 @@ register_block = BLOCKS.register
 
 
 def vector_f32(t: torch.Tensor) -> torch.Tensor:
-    """Norm weights and biases are read as float32 by every kernel, whatever they were stored as."""
-    return t.to(torch.float32).contiguous()
+    """Norm weights and biases are read as float32 by every kernel, whatever they were stored as.  Always a
+    copy of the part's own: a part may rewrite it (a norm whose weight is folded into a matrix)."""
+    return t.to(torch.float32).contiguous().clone()
 
 
 def matrix(t: torch.Tensor, rt: Runtime) -> torch.Tensor:

@@ -1,13 +1,7 @@
 """Arrangements of a layer's parts around the residual stream."""
 from __future__ import annotations
 
-import torch
-
-from .. import ops
-from .attention import Attention
-from .base import Block, RowStats, register_block
-from .mlp import SwiGLU
-from .norms import RMSNorm
+from .base import Block, as_delta, register_block
 
 
 @register_block("prenorm")
@@ -19,77 +13,34 @@ class PreNormBlock(Block):
     last delta on as `pending`, and the next norm (the next layer's, or the model's
     final one) adds it.
 
-    With few rows in bfloat16 (decoding), and when the parts are the built-in attention,
-    SwiGLU and RMSNorm, the adds and norms need no kernels of their own: the output and
-    down products add into the residual and leave each row's sums of squares
-    (`RowStats`) and a bfloat16 copy of it, and the QKV and gate/up products read that copy and
-    divide their output rows by the rows' rms.  For that the norms' weights are folded into the
-    columns of those two matrices once, when the block first runs ((x / rms * g) . W^T =
-    (x . (W g)^T) / rms), and the norms keep weights of one, so that every path, with few rows or
-    many, computes with the same folded matrices.  Eight launches per layer become five.
+    A part that said at bind time that it can take its norm into its own kernels
+    (`Part.fuse_norm`) is run through `forward_fused` for steps of up to its
+    `fused_rows` rows: it reads the residual's rounded copy and row statistics that the
+    part before it left (`RowStats`), adds its own delta into the residual and leaves the
+    same for the part after it, so that neither the norm nor the add needs a kernel of
+    its own.  Each half of the block decides for itself; a part without the protocol is
+    given normed rows and returns a delta, as ever.
     """
 
     graph_safe = True
-    FUSED_ROWS = 16
+    accepts_row_stats = True
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.fuse_mixer = bool(self.mixer.fuse_norm(self.mixer_norm))
+        self.fuse_feed_forward = bool(self.feed_forward.fuse_norm(self.ff_norm))
 
     def forward(self, ctx, residual, pending, cache, owns_cache=True):
-        if self._can_fuse(residual):
-            return self._forward_fused(ctx, residual, pending, cache, owns_cache)
         rt = ctx.rt
         t, d = residual.shape
+        if self.fuse_mixer and t <= self.mixer.fused_rows:
+            pending = self.mixer.forward_fused(ctx, residual, pending, self.mixer_norm, cache, owns_cache)
+        else:
+            xn = rt.workspace.get("block.normed", (t, d), rt.dtype)
+            self.mixer_norm.forward(residual, as_delta(pending), xn)
+            pending = self.mixer.forward(ctx, xn, cache, owns_cache)
+        if self.fuse_feed_forward and t <= self.feed_forward.fused_rows:
+            return self.feed_forward.forward_fused(ctx, residual, pending, self.ff_norm)
         xn = rt.workspace.get("block.normed", (t, d), rt.dtype)
-        self.mixer_norm.forward(residual, pending, xn)
-        mixed = self.mixer.forward(ctx, xn, cache, owns_cache)
-        self.ff_norm.forward(residual, mixed, xn)
+        self.ff_norm.forward(residual, as_delta(pending), xn)
         return self.feed_forward.forward(ctx, xn)
-
-    def _can_fuse(self, residual) -> bool:
-        fused = getattr(self, "_fusable", None)
-        if fused is None:
-            m, f = self.mixer, self.feed_forward
-            fused = self._fusable = (
-                type(m) is Attention and type(f) is SwiGLU and type(self.mixer_norm) is RMSNorm
-                and type(self.ff_norm) is RMSNorm and m.rt.dtype == torch.bfloat16
-                and (m.position is None or m.table is not None)
-                and m.hidden % 8 == 0 and m.qw % 8 == 0 and f.inter % 8 == 0
-                # matrices that the small-row products stream faster than the library does (measured: up to about
-                # 64 MB; a 7B model's gate/up and down matrices go through the library at twice the speed)
-                and all(w.numel() * w.element_size() <= ops.SMALL_M_MAX_WEIGHT_BYTES for w in (m.w_qkv, m.w_o, f.w_gate_up, f.w_down))
-            )
-            if fused:
-                self._fold_norm_weights()
-        return fused and residual.shape[0] <= self.FUSED_ROWS
-
-    def _fold_norm_weights(self) -> None:
-        """W[n][k] *= g[k] for the matrices that read a norm's output, in float32 and rounded once; g becomes 1."""
-        for norm, matrix in ((self.mixer_norm, self.mixer.w_qkv), (self.ff_norm, self.feed_forward.w_gate_up)):
-            if getattr(norm, "folded", False):
-                continue  # a block that runs twice, or norms shared between blocks, fold once
-            matrix.copy_((matrix.float() * norm.weight.float()[None, :]).to(matrix.dtype))
-            norm.weight.fill_(1.0)
-            norm.folded = True
-
-    def _forward_fused(self, ctx, residual, pending, cache, owns_cache):
-        rt, m, f = ctx.rt, self.mixer, self.feed_forward
-        ws = rt.workspace
-        t, d = residual.shape
-        nb = ops.gemm_small_m_stats_blocks(d)
-        store = owns_cache and m.has_kv
-        width = m.qkv_width(store)
-        qkv = ws.get("attn.qkv", (t, width), rt.dtype)
-        xcopy = ws.get("block.residual_copy", (t, d), rt.dtype)
-        if isinstance(pending, RowStats) and pending.copy is not None:
-            ops.gemm_small_m_scaled(pending.copy, pending.stats, pending.blocks, self.mixer_norm.eps, m.w_qkv[:width], None, qkv)
-        else:  # the first block after the embedding, or after a block of another kind
-            xn = ws.get("block.normed", (t, d), rt.dtype)
-            self.mixer_norm.forward(residual, pending, xn)
-            ops.linear(xn, m.w_qkv[:width], None, qkv)
-        attended = ws.get("attn.out", (t, m.qw), rt.dtype)
-        m.encode_attend(ctx, qkv, cache, store, attended)
-        stats = ws.get("block.stats_mixer", (t, nb), torch.float32)
-        ops.gemm_small_m_resadd(attended, m.w_o, residual, stats, xcopy)
-        h = ws.get("ffn.h", (t, f.inter), rt.dtype)
-        ops.gemm_small_m_scaled(xcopy, stats, nb, self.ff_norm.eps, f.w_gate_up[: f.inter], f.w_gate_up[f.inter :], h)
-        stats = ws.get("block.stats_ffn", (t, nb), torch.float32)
-        ops.gemm_small_m_resadd(h, f.w_down, residual, stats, xcopy)
-        return RowStats(stats, nb, xcopy)

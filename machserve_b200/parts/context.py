@@ -2,11 +2,11 @@
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional
+from typing import Dict, Hashable, List, Optional
 
 import torch
 
-from .base import Runtime
+from .base import Runtime, Work
 
 
 @dataclass
@@ -34,17 +34,9 @@ class StepContext:
     block_tables: Dict[int, torch.Tensor]  # cache group -> [slots, max_pages] page ids by request slot, -1 where none
     want_rows: torch.Tensor  # [W] rows whose logits are wanted
     num_wanted: int
-    # the rows sorted by how they are attended: rows that are alone in their sequence (decoding), and
-    # tiles of up to 64 consecutive rows of one sequence (portions of prompts)
-    single_rows: Optional[torch.Tensor] = None  # [num_single]
-    num_single: int = 0
-    tile_row0: Optional[torch.Tensor] = None  # [num_tiles] first row of a tile
-    tile_rows: Optional[torch.Tensor] = None  # [num_tiles] rows in it
-    num_tiles: int = 0
-    big_tile_row0: Optional[torch.Tensor] = None  # the same portions cut into tiles of up to 128 rows
-    big_tile_rows: Optional[torch.Tensor] = None
-    num_big_tiles: int = 0
-    # the same on the host, for parts that plan their launches or loop over sequences
+    # the work lists that parts asked for (`Part.plan_key`, `Part.plan`), staged with the arrays above
+    work: Dict[Hashable, Work] = field(default_factory=dict)
+    # the sequences on the host, for parts that plan their launches or loop over sequences
     host_cu_tokens: List[int] = field(default_factory=list)
     host_seq_start: List[int] = field(default_factory=list)
     host_state_slots: List[int] = field(default_factory=list)
@@ -55,12 +47,19 @@ class StepContext:
 
 @dataclass
 class PagedBinding:
-    """The pages of one run of a layer: [num_pages, kv_heads, page_size, head_dim] each."""
+    """The pages of one run of a layer, plane by plane: [num_pages, heads, page_size, width] each."""
 
     group: int
-    k_pages: torch.Tensor
-    v_pages: torch.Tensor
+    planes: Dict[str, torch.Tensor]
     window: Optional[int]
+
+    @property
+    def k_pages(self) -> torch.Tensor:
+        return self.planes["k"]
+
+    @property
+    def v_pages(self) -> torch.Tensor:
+        return self.planes["v"]
 
     def block_table(self, ctx: StepContext) -> torch.Tensor:
         return ctx.block_tables[self.group]

@@ -5,10 +5,11 @@ import torch
 
 from .. import ops
 from ..weights.loader import TensorDecl
-from .base import Part, matrix
+from .base import Head, TokenEmbedding, matrix, register_embedding, register_head
 
 
-class Embedding(Part):
+@register_embedding("embedding")
+class Embedding(TokenEmbedding):
     """x[r, :] = E[token[r], :] into the float32 residual stream, no scaling
     (crates/mach-model/src/kernels.rs:578-585 of gqf2008/machserve).
 
@@ -32,7 +33,8 @@ class Embedding(Part):
         return ops.embed_gather(self.table, ctx.token_ids, out)
 
 
-class LMHead(Part):
+@register_head("lm_head")
+class LMHead(Head):
     """logits = x . W^T in float32, for the rows that are asked for only (the reference computes
     every row, crates/mach-model/src/batched.rs:4594-4626).  With `tied_to` set, the head's own
     tensor may be absent and the embedding table stands in
@@ -54,12 +56,12 @@ class LMHead(Part):
             out.append(TensorDecl(self.tied_to, (self.vocab, self.hidden)))
         return out
 
-    def bind(self, tensors, rt, shared=None):
-        super().bind(tensors, rt)
+    def bind(self, tensors, rt, embedding=None):
+        super().bind(tensors, rt, embedding)
         if self.name in tensors:
             self.weight = matrix(tensors[self.name], rt)
-        elif shared is not None:
-            self.weight = shared  # the embedding's own device tensor: one copy in memory
+        elif embedding is not None and getattr(embedding, "name", None) == self.tied_to and hasattr(embedding, "table"):
+            self.weight = embedding.table  # the embedding's own device tensor: one copy in memory
         else:
             self.weight = matrix(tensors[self.tied_to], rt)
 

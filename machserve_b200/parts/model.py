@@ -12,8 +12,7 @@ import torch
 
 from ..config.spec import LayerSpec, ModelSpec
 from ..weights.loader import TensorDecl
-from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, CacheNeed, Runtime
-from .embedding import Embedding, LMHead
+from .base import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, Block, CacheNeed, Part, Runtime, as_delta
 
 
 def build_block(layer: LayerSpec) -> Block:
@@ -32,18 +31,17 @@ def build_block(layer: LayerSpec) -> Block:
 class DecoderModel:
     def __init__(self, spec: ModelSpec):
         self.spec = spec
-        self.embedding = Embedding(spec.embedding)
+        self.embedding = EMBEDDINGS.build(spec.embedding)
         self.blocks: List[Block] = [build_block(l) for l in spec.layers]
         self.final_norm = NORMS.build(spec.final_norm)
-        self.head = LMHead(spec.head)
+        self.head = HEADS.build(spec.head)
         self.rt: Optional[Runtime] = None
 
     # -- what the model reads and what it needs of the cache ------------------
 
     def tensors(self) -> List[TensorDecl]:
         out, seen = [], {}
-        parts = [self.embedding, *[p for b in self.blocks for p in b.parts()], self.final_norm, self.head]
-        for part in parts:
+        for part in self.parts():
             for d in part.tensors():
                 prev = seen.get(d.name)
                 if prev is None:
@@ -54,6 +52,9 @@ class DecoderModel:
                 elif d.required and not prev.required:
                     out[out.index(prev)] = seen[d.name] = d
         return out
+
+    def parts(self) -> List[Part]:
+        return [self.embedding, *[p for b in self.blocks for p in b.parts()], self.final_norm, self.head]
 
     def cache_needs(self) -> List[CacheNeed]:
         """For every entry of the run order: the cache its run owns, or None if it owns none."""
@@ -73,8 +74,7 @@ class DecoderModel:
 
     def graph_safe(self) -> bool:
         """Whether a decoding step of this model may be captured in a CUDA graph: every part says so."""
-        parts = [self.embedding, *[p for b in self.blocks for p in b.parts()], self.final_norm, self.head]
-        return all(p.graph_safe for p in parts) and all(getattr(b, "graph_safe", False) for b in self.blocks)
+        return all(p.graph_safe for p in self.parts()) and all(getattr(b, "graph_safe", False) for b in self.blocks)
 
     # -- weights ----------------------------------------------------------------
 
@@ -82,11 +82,9 @@ class DecoderModel:
         self.rt = rt
         self.embedding.bind(tensors, rt)
         for b in self.blocks:
-            for p in b.parts():
-                p.bind(tensors, rt)
+            b.bind(tensors, rt)
         self.final_norm.bind(tensors, rt)
-        tied = self.head.tied_to == self.embedding.name
-        self.head.bind(tensors, rt, shared=self.embedding.table if tied else None)
+        self.head.bind(tensors, rt, self.embedding)
 
     # -- one step ---------------------------------------------------------------
 
@@ -101,10 +99,13 @@ class DecoderModel:
         self.embedding.forward(ctx, residual)
         pending = None
         for i, run in enumerate(spec.run_order):
-            pending = self.blocks[run.layer].forward(ctx, residual, pending, caches[i], run.cache_of is None)
+            block = self.blocks[run.layer]
+            if not block.accepts_row_stats:
+                pending = as_delta(pending)  # a block of another kind sees a delta or None, as every norm does
+            pending = block.forward(ctx, residual, pending, caches[i], run.cache_of is None)
         w = ctx.want_rows.shape[0]
         final = ws.get("model.final", (w, spec.hidden_size), rt.dtype)
-        self.final_norm.forward(residual, pending, final, rows=ctx.want_rows)
+        self.final_norm.forward(residual, as_delta(pending), final, rows=ctx.want_rows)
         logits = ws.get("model.logits", (w, spec.vocab_size), torch.float32)
         return self.head.forward(ctx, final, logits)
 

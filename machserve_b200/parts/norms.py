@@ -3,7 +3,7 @@ from __future__ import annotations
 
 from .. import ops
 from ..weights.loader import TensorDecl
-from .base import Norm, RowStats, register_norm, vector_f32
+from .base import Norm, as_delta, register_norm, vector_f32
 
 
 @register_norm("rmsnorm")
@@ -28,6 +28,10 @@ class RMSNorm(Norm):
         self.weight = vector_f32(tensors[self.name])
 
     def forward(self, residual, delta, out, rows=None):
-        if isinstance(delta, RowStats):
-            delta = None  # already added to the residual by the kernel that produced it
-        return ops.add_rmsnorm(residual, delta, self.weight, out, self.eps, rows)
+        return ops.add_rmsnorm(residual, as_delta(delta), self.weight, out, self.eps, rows)
+
+    def fold_into(self, matrix):
+        """W[n][k] *= g[k], in float32 and rounded once; g becomes 1 ((x / rms * g) . W^T = (x . (W g)^T) / rms)."""
+        matrix.copy_((matrix.float() * self.weight[None, :]).to(matrix.dtype))
+        self.weight.fill_(1.0)
+        return True

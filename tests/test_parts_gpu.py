@@ -79,7 +79,12 @@ def test_parts_alone(model_root, name, dtype):
     block.mixer_norm.forward(res, torch.tensor(delta, dtype=tdt, device=rt.device), out)
     summed = x.astype(np.float32).astype(np.float64) + dr
     assert_close(_n(res), summed, 1e-6, "residual after the add")
-    assert_close(_n(out), rms_norm(summed, w[prefix + "input_layernorm.weight"], cfg["rms_norm_eps"]), tol / 4, "norm")
+    # In bfloat16 a part that takes its norm into its own kernels has the norm's weight folded into the columns of
+    # its first matrix, and the norm keeps a weight of one: norm and part together compute what they always did.
+    assert block.fuse_mixer == block.fuse_feed_forward == bf16
+    g1 = w[prefix + "input_layernorm.weight"]
+    g2 = w[prefix + "post_attention_layernorm.weight"]
+    assert_close(_n(out), rms_norm(summed, np.ones_like(g1) if bf16 else g1, cfg["rms_norm_eps"]), tol / 4, "norm")
 
     # rotary table against the plain angles
     table = block.mixer.position.rotary_table(rt)
@@ -92,14 +97,15 @@ def test_parts_alone(model_root, name, dtype):
     from tests.plain.model import layer_window
 
     got = _n(block.mixer.forward(ctx, xn_t, runner.bindings[layer]))
+    xa, xf = (xr * g1, xr * g2) if bf16 else (xr, xr)  # what the folded matrices stand for
     want = np.concatenate([
-        attention_block(xr[:19], w, prefix, cfg, positions[:19], layer_window(cfg, layer)),
-        attention_block(xr[19:], w, prefix, cfg, positions[19:], layer_window(cfg, layer)),
+        attention_block(xa[:19], w, prefix, cfg, positions[:19], layer_window(cfg, layer)),
+        attention_block(xa[19:], w, prefix, cfg, positions[19:], layer_window(cfg, layer)),
     ])
     assert_close(got, want, tol, "attention mixer")
     got = _n(block.feed_forward.forward(ctx, xn_t))
     m = prefix + "mlp."
-    assert_close(got, swiglu(xr, w[m + "gate_proj.weight"], w[m + "up_proj.weight"], w[m + "down_proj.weight"]), tol, "feed-forward")
+    assert_close(got, swiglu(xf, w[m + "gate_proj.weight"], w[m + "up_proj.weight"], w[m + "down_proj.weight"]), tol, "feed-forward")
 
     # the block: residual in, residual + both deltas out (the last delta is handed on, not yet added)
     res = torch.tensor(x, dtype=torch.float32, device=rt.device)
@@ -350,7 +356,7 @@ def test_toy_parts_are_registered_built_and_stepped(tmp_path):
         runner = _runner(d, "float32", page=8, tokens=192)
         assert not runner.use_graphs  # the toy mixer loops on the host: its steps are never captured
         needs = runner.model.cache_needs()
-        assert [type(n).__name__ if n else None for n in needs] == ["PagedKV", "FixedState", "PagedKV", "FixedState", None]
+        assert [type(n).__name__ if n else None for n in needs] == ["PagedCache", "FixedState", "PagedCache", "FixedState", None]
         assert len(runner.cache.groups) == 1 and runner.cache.groups[0].runs == [0, 2] and sorted(runner.states) == [1, 3]
 
         a, b = random_tokens(90, 45, 1), random_tokens(90, 30, 2)
