@@ -267,7 +267,7 @@ class ModelRunner:
                 rec[i, : len(table)] = table
             dev = self._row_device[at : at + n * words]
             dev.copy_(self._row_pinned[turn][at : at + n * words], non_blocking=True)
-            self.tables[g].index_copy_(0, dev[:n], dev[n:].view(n, self.max_pages))
+            self.tables[g].index_copy_(0, dev[:n].long(), dev[n:].view(n, self.max_pages))
             self.h2d_bytes += 4 * n * words
         ev = torch.cuda.Event()
         ev.record()
