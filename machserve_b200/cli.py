@@ -5,7 +5,9 @@ The reference is configured by environment variables of its server
 their names and meanings: --capacity (MACH_CAPACITY, 64), --prefill-rows
 (MACH_PREFILL_ROWS, 512), --dtype (MACH_DTYPE: f32, or bf16 where it has f16),
 --tpp (MACH_TPP, tokens per page, 64), --max-seq (MACH_MAX_SEQ).  Sampling options
-are the fields of its SamplingParams.  The library itself reads no environment.
+are the fields of its SamplingParams.  The library itself reads no environment, except for where to find
+nvcc (NVCC, CUDA_HOME) and where to put the built kernels when the tree cannot be written
+(MACHSERVE_B200_BUILD_DIR), both in csrc/build.py.
 """
 from __future__ import annotations
 
@@ -85,10 +87,23 @@ def cmd_random(a) -> int:
 
 
 def cmd_bench(a) -> int:
+    """Decode and prefill throughput of a shape with random weights, or of a model folder: the repository's bench.py
+    with its options under this command's names."""
+    import os
     import runpy
     from pathlib import Path
 
-    sys.argv = ["bench.py", *a.rest]
+    batches = [int(b) for b in a.batch.split(",") if b.strip()]
+    argv = ["bench.py", "--batch", str(batches[0]), "--points", ",".join(str(b) for b in batches[1:]), "--context", str(a.ctx),
+            "--prefill", str(a.prefill), "--steps", str(a.steps), "--warmup", str(a.warmup), "--only", "headline",
+            "--dtype", "f32" if a.fp32 else a.dtype]
+    if os.path.isdir(a.target):
+        argv += ["--model", a.target]
+    else:
+        argv += ["--shape", a.target.lower()]
+    if a.layers:
+        argv += ["--layers", str(a.layers)]
+    sys.argv = argv
     runpy.run_path(str(Path(__file__).resolve().parent.parent / "bench.py"), run_name="__main__")
     return 0
 
@@ -133,8 +148,16 @@ def main(argv=None) -> int:
     w.add_argument("--norm-std", type=float, default=0.05)
     w.set_defaults(fn=cmd_random)
 
-    b = sub.add_parser("bench", help="the repository's bench.py (decode and prefill throughput)")
-    b.add_argument("rest", nargs=argparse.REMAINDER)
+    b = sub.add_parser("bench", help="decode and prefill throughput of a shape (random weights) or of a model folder")
+    b.add_argument("target", help="qwen2.5-0.5b, qwen2.5-1.5b, qwen2.5-7b, or a folder with config.json and model.safetensors")
+    b.add_argument("--batch", default="8,1,64", help="batch sizes, comma separated; the first is the headline")
+    b.add_argument("--ctx", type=int, default=2048, help="tokens every request holds when decoding is timed")
+    b.add_argument("--prefill", type=int, default=2048, help="tokens of the timed prompt")
+    b.add_argument("--fp32", action="store_true", help="the true 32-bit path")
+    b.add_argument("--dtype", default="bf16", choices=["bf16", "bfloat16", "f32", "float32"])
+    b.add_argument("--steps", type=int, default=50)
+    b.add_argument("--warmup", type=int, default=5)
+    b.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (named in the output)")
     b.set_defaults(fn=cmd_bench)
 
     a = ap.parse_args(argv)

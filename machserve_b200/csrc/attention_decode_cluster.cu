@@ -96,8 +96,6 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [16][STRIDE]
   __nv_bfloat16* kv_s = q_s + 16 * STRIDE;                           // [stages][K, V][DCL_TILE][STRIDE]
   __shared__ float fin_m[16], fin_l[16];
-
-  MS_TIMELINE_BEGIN(200);
   ms_pdl_trigger();
   // everything up to the wait reads only what no kernel of this step writes: the step's index arrays,
   // the block tables, and keys and values of positions before the current one
@@ -124,7 +122,6 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
                      first_key, pos, pos, tid);
 
   ms_pdl_wait();
-  MS_TIMELINE_WAITED();
 
   const int ptile = pos / DCL_TILE;
   bool row_done = false;  // the current position's key and value are in place (fused form)
@@ -224,8 +221,6 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
     }
     ms_cp_async_commit();
   }
-
-  MS_TIMELINE_MARK(0);
   MsRowState<HD> st;
   st.init();
   unsigned qa[HD / 16][4];
@@ -259,7 +254,6 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
     }
   }
   __syncthreads();  // the stages are used for the merge next
-  MS_TIMELINE_MARK(1);
 
   // merge the four warps of the block in warp order
 #pragma unroll
@@ -314,9 +308,7 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
   // share of the (head, coordinate) pairs, and a thread first requests all it needs from the other blocks
   // (independent loads, one round trip) and then adds in rank order, so the result does not depend on timing.
   cg::cluster_group cluster = cg::this_cluster();
-  MS_TIMELINE_MARK(2);
   cluster.sync();
-  MS_TIMELINE_MARK(3);
   {
     const int total = groups * HD;
     const int per = (total + num_splits - 1) / num_splits;
@@ -344,7 +336,6 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
       if (live) out[((size_t)t * hq + kvh * groups + r) * HD + d] = __float2bfloat16_rn(l > 0.f ? __fdividef(o, l) : 0.f);
     }
   }
-  MS_TIMELINE_MARK(4);
   cluster.sync();  // a block's shared memory must live until the others have read it
 }
 
@@ -416,7 +407,6 @@ static int launch_decode_cluster(const void* q, DclRaw raw, const void* k_pages,
 #undef MS_DCL_LAUNCH
 }
 
-MS_TIMELINE_SETTER(ms_timeline_set_attention_decode_cluster)
 
 // The most tiles a block can hold at once for a head size (about 100 KB of shared memory).
 MS_API int ms_attention_decode_cluster_max_stages(int hd) {

@@ -186,24 +186,6 @@ __device__ __forceinline__ void atc_row_probs(const unsigned (&r)[ATC_KEYS], int
   }
 }
 
-// Diagnostics, compiled only with -DATC_TIMING: per key tile of block (0, 0) the clock at six points of softmax
-// thread 0 (g_atc_times) and at points of the issuing (columns 0-4) and the copying thread (5, 6) (g_atc_times2);
-// and every block's start and end in nanoseconds, its SM and its number of tiles (g_atc_blocks).
-#ifdef ATC_TIMING
-__device__ long long g_atc_times[64 * 8];
-__device__ long long g_atc_times2[64 * 8];
-#define ATC_STAMP2(t, k) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (t) < 64) g_atc_times2[(t) * 8 + (k)] = clock64(); } while (0)
-__device__ unsigned long long g_atc_blocks[4096 * 4];
-__device__ __forceinline__ unsigned long long atc_now() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-#define ATC_STAMP(t, k) do { if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && (t) < 64) g_atc_times[(t) * 8 + (k)] = clock64(); } while (0)
-#else
-#define ATC_STAMP(t, k) do { } while (0)
-#define ATC_STAMP2(t, k) do { } while (0)
-#endif
 
 struct AtcShared {
   unsigned long long q_full, k_full, k_empty, v_full[2], v_empty[2], s_full, s_free, p_full, o_full;
@@ -236,9 +218,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   unsigned char* p_s = k_s + KV_BYTES;       // two panels
   volatile int* abort_flag = &sh->abort_flag;
 
-#ifdef ATC_TIMING
-  const unsigned long long atc_t0 = atc_now();
-#endif
   const int tile_id = gridDim.x - 1 - blockIdx.x;  // the longest tiles first
   const int row0 = tile_row0[tile_id], nrows = tile_rows[tile_id];
   const int h = blockIdx.y, kvh = h / (hq / hkv);
@@ -316,11 +295,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
         for (int p = 0; p < PANELS; ++p) atc_tma_2d(atc_smem(k_s + p * PANEL_BYTES + r * 128), &map_k, p * 64, grow, atc_smem(&sh->k_full));
       }
-      ATC_STAMP2(t, 5);
       // values: two stages
       if (t >= 2 && !atc_mbar_wait(atc_smem(&sh->v_empty[s]), ((t >> 1) - 1) & 1, abort_flag, 11)) break;
       atc_mbar_expect_tx(atc_smem(&sh->v_full[s]), bytes);
-      ATC_STAMP2(t, 6);
       for (int r = 0; r < ATC_KEYS; r += box) {
         const int key = key0 + r;
         if (key > pos_last || key + box - 1 < first_key) continue;
@@ -347,7 +324,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       if (!atc_mbar_wait(atc_smem(&sh->p_full), j & 1, abort_flag, 14) ||
           !atc_mbar_wait(atc_smem(&sh->v_full[s]), (j >> 1) & 1, abort_flag, 14))
         return false;
-      ATC_STAMP2(j, 3);
       atc_fence_after();
 #pragma unroll
       for (int k = 0; k < ATC_KEYS / 16; ++k) {
@@ -359,16 +335,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       atc_commit(atc_smem(&sh->v_empty[s]));
       atc_commit(atc_smem(&sh->o_full));
-      ATC_STAMP2(j, 4);
       return true;
     };
     for (int t = 0; t < ntiles && ok; ++t) {
       ok = atc_mbar_wait(atc_smem(&sh->k_full), t & 1, abort_flag, 13);
-      ATC_STAMP2(t, 0);
       // the scores of the tile before have left tensor memory for the softmax threads' registers
       if (ok && t >= 1) ok = atc_mbar_wait(atc_smem(&sh->s_free), (t - 1) & 1, abort_flag, 16);
       if (!ok) break;
-      ATC_STAMP2(t, 1);
       atc_fence_after();
       // S = Q K^T over hd in steps of 16 (four steps per 64-column panel)
 #pragma unroll
@@ -378,7 +351,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       atc_commit(atc_smem(&sh->k_empty));
       atc_commit(atc_smem(&sh->s_full));
-      ATC_STAMP2(t, 2);
       // the product of the tile before follows the scores of this one: its probabilities are written while
       // these scores are computed
       if (t >= 1) ok = issue_pv(t - 1);
@@ -394,18 +366,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     float m = -INFINITY, l = 0.f;  // the reference of the row's exponents, the sum of its probabilities
     bool ok = true;
     for (int t = 0; t < ntiles && ok; ++t) {
-      ATC_STAMP(t, 0);
       ok = atc_mbar_wait(atc_smem(&sh->s_full), t & 1, abort_flag, 15);
       if (!ok) break;
       atc_fence_after();
-      ATC_STAMP(t, 1);
       unsigned r[ATC_KEYS];
 #pragma unroll
       for (int c = 0; c < ATC_KEYS; c += 32) atc_ld32_issue(tmem_s + lane_addr + c, r + c);
       atc_wait_ld();
       atc_fence_before();
       atc_mbar_arrive(atc_smem(&sh->s_free));
-      ATC_STAMP(t, 2);
       const int key0 = (tile_lo + t) * ATC_KEYS;
       const int rlo = lo - key0, rhi = hi - key0;
       // whether every row of this warp sees the whole tile: the same for the whole warp, which keeps the
@@ -419,14 +388,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const bool rescale = __any_sync(0xffffffffu, grow && m != -INFINITY);
       m = grow ? mx : m;
       const float mu = m == -INFINITY ? 0.f : m;
-      ATC_STAMP(t, 3);
       // P V of the tile before is done: the tile of P is free and O is complete up to that tile
       if (t >= 1) {
         ok = atc_mbar_wait(atc_smem(&sh->o_full), (t - 1) & 1, abort_flag, 15);
         if (!ok) break;
         atc_fence_after();
       }
-      ATC_STAMP(t, 4);
       unsigned long long sum2[2] = {atc_pack(0.f, 0.f), atc_pack(0.f, 0.f)};
       if (inside) {
         atc_row_probs<true, 0>(r, rlo, rhi, scale_log2, mu, p_s, row, sum2);
@@ -453,7 +420,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the tensor core reads P through the async proxy
       atc_mbar_arrive(atc_smem(&sh->p_full));
-      ATC_STAMP(t, 5);
     }
     if (ok && ntiles > 0) {
       ok = atc_mbar_wait(atc_smem(&sh->o_full), (ntiles - 1) & 1, abort_flag, 15);
@@ -494,19 +460,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     __syncthreads();
   }
   if (warp == 5) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(256) : "memory");
-#ifdef ATC_TIMING
-  if (tid == 0) {
-    const int b = blockIdx.y * gridDim.x + blockIdx.x;
-    unsigned smid;
-    asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
-    if (b < 4096) {
-      g_atc_blocks[b * 4] = atc_t0;
-      g_atc_blocks[b * 4 + 1] = atc_now();
-      g_atc_blocks[b * 4 + 2] = smid;
-      g_atc_blocks[b * 4 + 3] = (unsigned long long)ntiles;
-    }
-  }
-#endif
 }
 
 // ------------------------------------------------------------------------------------ host
@@ -566,11 +519,6 @@ MS_API int ms_attention_tc_status(int reset) {
   return v;
 }
 
-#ifdef ATC_TIMING
-MS_API void ms_atc_times(long long* out) { cudaMemcpyFromSymbol(out, g_atc_times, sizeof(long long) * 64 * 8); }
-MS_API void ms_atc_times2(long long* out) { cudaMemcpyFromSymbol(out, g_atc_times2, sizeof(long long) * 64 * 8); }
-MS_API void ms_atc_blocks(unsigned long long* out) { cudaMemcpyFromSymbol(out, g_atc_blocks, sizeof(unsigned long long) * 4096 * 4); }
-#endif
 
 // A wait that runs out, in the form that cannot hang: one thread waits `polls` polls on a barrier in its own
 // shared memory that nothing arrives on, through the helper that every wait of the kernel above uses; no

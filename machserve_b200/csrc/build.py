@@ -34,9 +34,6 @@ NVCC_FLAGS = [
     "-fvisibility=hidden",
 ]
 # No fast-math flag on purpose: expf, rsqrtf and division keep their accurate forms.
-# MACHSERVE_B200_NVCC_EXTRA: further flags, e.g. -DMS_TIMELINE for the device-side kernel timeline (launch.cuh);
-# they are part of the stamp, so a build with other flags is not mistaken for this one.
-NVCC_FLAGS += os.environ.get("MACHSERVE_B200_NVCC_EXTRA", "").split()
 
 
 class BuildError(RuntimeError):

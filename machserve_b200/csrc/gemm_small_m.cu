@@ -117,7 +117,6 @@ gemm_small_m_kernel(const void* __restrict__ x_any, int ldx, const __nv_bfloat16
                     void* __restrict__ out, int ldo, int M, int K, GsmShape sh, GsmExtra ex) {
   constexpr int THREADS = W * 32, WR = W / RB, COLS = MT * 8;
   constexpr int TPR = THREADS / COLS;  // threads that share a row of the activations: 4 .. 32, within one warp
-  MS_TIMELINE_BEGIN(100 + EPI * 10 + SCALE);
   extern __shared__ __align__(16) uint4 gsm_dyn[];
   // dynamic: [warp][staged][rows 0..7 | rows 8..15][lane] weights; then (XS) activations [COLS][xs_stride]
   // bfloat16
@@ -173,7 +172,6 @@ gemm_small_m_kernel(const void* __restrict__ x_any, int ldx, const __nv_bfloat16
   }
   ms_pdl_trigger();
   ms_pdl_wait();
-  MS_TIMELINE_WAITED();
 
   // the residual epilogue's own elements of the old residual, requested now so that they are there when the sum is
   constexpr int OUT_ELEMS = RB * 16 * COLS;
@@ -224,7 +222,6 @@ gemm_small_m_kernel(const void* __restrict__ x_any, int ldx, const __nv_bfloat16
   }
   asm volatile("cp.async.wait_group 0;\n" ::: "memory");  // staged weights: a thread reads only what it copied itself
   if (XS || SCALE) __syncthreads();
-  MS_TIMELINE_MARK(0);
 
   if (XS) {
     // the B fragments of the warp's u-th chunk come from shared memory
@@ -273,7 +270,6 @@ gemm_small_m_kernel(const void* __restrict__ x_any, int ldx, const __nv_bfloat16
         gsm_chunk<MT>(acc, wa[u], wb[u], x, ldx, M, K, (ch0 + (u1 + u) * stride) * 32, g, c);
     }
   }
-  MS_TIMELINE_MARK(2);
 
   // add the warps that share rows, in warp order
 #pragma unroll
@@ -315,7 +311,6 @@ gemm_small_m_kernel(const void* __restrict__ x_any, int ldx, const __nv_bfloat16
     if (rank != 0) return;
   }
   __syncthreads();
-  MS_TIMELINE_MARK(3);
 
   if (EPI == GSM_EPI_RESADD) {
     // residual[m][n] += product, in place (each element belongs to one thread of one block); then the sum of
@@ -496,7 +491,6 @@ static int gsm_dispatch(const void* x, int ldx, const void* w_lo, const void* w_
 #undef GSM_CASE
 }
 
-MS_TIMELINE_SETTER(ms_timeline_set_gemm_small_m)
 
 MS_API int ms_gemm_small_m_supports(int M, int N, int K) { return M >= 1 && M <= 64 && N >= 1 && K >= 8 && K % 8 == 0; }
 

@@ -61,6 +61,37 @@ class StepEntry:
     from_sampled: Optional[int] = None
 
 
+SCRATCH_MARGIN_BYTES = 256 << 20  # for scratch memory, the library's workspace and the kernels themselves
+
+
+def estimate_device_bytes(model: DecoderModel, dtype: torch.dtype, page_size: int, num_pages: int, max_requests: int,
+                          max_seq_len: int) -> Dict[str, int]:
+    """What a runner of this model will hold on the device, from the parts' declarations alone: every tensor once
+    (matrices in the runtime's dtype, vectors in float32), the pages of every cache group, the state arrays, the
+    block tables, and a margin of 256 MiB (the reference estimates the same before it allocates,
+    crates/mach-server/src/startup.rs:344-419 of gqf2008/machserve)."""
+    elt = 4 if dtype == torch.float32 else 2
+    weights = 0
+    for d in model.tensors():
+        n = 1
+        for s in d.shape:
+            n *= int(s)
+        if d.random or d.required:  # a tied head's own tensor is absent and costs nothing
+            weights += n * (4 if d.init == "table" or len(d.shape) < 2 else elt)
+    cache = CacheManager(model.cache_needs(), page_size, num_pages, max_requests)
+    pages = sum(len(g.runs) * g.pool.size * page_size * g.need.elements_per_token() * elt for g in cache.groups)
+    states = 0
+    for need in cache.state_runs.values():
+        n = max_requests * 4
+        for s in need.shape:
+            n *= int(s)
+        states += n
+    tables = len(cache.groups) * max_requests * (-(-max_seq_len // page_size)) * 4
+    total = weights + pages + states + tables + SCRATCH_MARGIN_BYTES
+    return {"weights_bytes": weights, "cache_bytes": pages, "state_bytes": states, "table_bytes": tables,
+            "margin_bytes": SCRATCH_MARGIN_BYTES, "total_bytes": total}
+
+
 class StepError(ValueError):
     """The step as given cannot run (unknown token id, too many tokens, context too long)."""
 
@@ -92,6 +123,17 @@ class ModelRunner:
         self.rt = Runtime(self.dtype, self.device, Workspace(self.device), self.max_seq_len,
                           torch.cuda.get_device_properties(self.device).multi_processor_count)
         self.model = DecoderModel(self.spec)
+        # before anything is allocated: does it fit?  (weights that are on the device already are not needed twice)
+        plan = estimate_device_bytes(self.model, self.dtype, page_size, num_pages, max_requests, self.max_seq_len)
+        resident = sum(t.numel() * t.element_size() for t in tensors.values() if t.is_cuda)
+        free, total = torch.cuda.mem_get_info(self.device)
+        if plan["total_bytes"] - min(resident, plan["weights_bytes"]) > free:
+            gib = lambda b: f"{b / 2**30:.2f} GiB"
+            raise RuntimeError(
+                f"the model does not fit on {self.device}: weights {gib(plan['weights_bytes'])} + cache {gib(plan['cache_bytes'])} "
+                f"({num_pages} pages of {page_size} tokens) + states {gib(plan['state_bytes'])} + margin {gib(plan['margin_bytes'])} "
+                f"= {gib(plan['total_bytes'])}, of which {gib(resident)} are on the device already; {gib(free)} of {gib(total)} are free. "
+                "Use fewer pages (num_pages), a smaller capacity or a shorter max_seq.")
         on_device = {n: t.to(self.device) for n, t in tensors.items()}
         self.model.bind(on_device, self.rt)
         del on_device

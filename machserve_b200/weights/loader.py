@@ -14,6 +14,7 @@ float32 instead.
 """
 from __future__ import annotations
 
+import warnings
 from dataclasses import dataclass
 from typing import Dict, Iterable, Optional, Tuple
 
@@ -111,6 +112,11 @@ def load_weights(
         for n in decls:
             if n in entries:
                 out[n] = _stored_to_kept(entries[n].file.tensor(n), dtype).to(device)
+        halves = [n for n in out if entries[n].dtype == "F16"]
+        if halves and dtype != torch.float32:
+            # float16 has three more bits of mantissa than bfloat16 and a narrower range: said once, not silently
+            warnings.warn(f"{model_dir}: {len(halves)} tensors are stored as float16 and are rounded to bfloat16 "
+                          f"(first: {halves[0]}); load with dtype float32 to keep every bit", stacklevel=2)
         return out
     finally:
         for f in files:

@@ -15,7 +15,7 @@ import json
 import mmap
 import struct
 from pathlib import Path
-from typing import Dict, Iterable, List, Tuple
+from typing import Dict, Iterable, List, Optional, Tuple
 
 import numpy as np
 import torch
@@ -136,20 +136,77 @@ class SafetensorsFile:
         self._fh.close()
 
 
+INDEX_NAME = "model.safetensors.index.json"
+
+
+def read_shard_index(folder: Path) -> Optional[Tuple[Dict[str, str], Optional[int]]]:
+    """(tensor name -> shard file name, the total size it states or None) from a folder's
+    `model.safetensors.index.json`, or None if there is none.
+    A shard must be a `.safetensors` file that lies in the folder itself (no path may lead out of it) and exists
+    (crates/mach-model/src/loader.rs:327-384 of gqf2008/machserve)."""
+    path = folder / INDEX_NAME
+    if not path.is_file():
+        return None
+    try:
+        raw = json.loads(path.read_text())
+    except (OSError, ValueError) as e:
+        raise SafetensorsError(f"{path}: cannot be read as JSON: {e}") from None
+    weight_map = raw.get("weight_map") if isinstance(raw, dict) else None
+    if not isinstance(weight_map, dict):
+        raise SafetensorsError(f"{path}: 'weight_map' is missing or is not an object")
+    out = {}
+    for name, shard in weight_map.items():
+        if not isinstance(shard, str) or not shard.endswith(".safetensors") or Path(shard).name != shard or shard in (".", ".."):
+            raise SafetensorsError(f"{path}: weight_map['{name}'] must name a .safetensors file of this folder, found {shard!r}")
+        if not (folder / shard).is_file():
+            raise SafetensorsError(f"{path}: the shard {shard} that it names is missing")
+        out[name] = shard
+    total = raw.get("metadata", {}).get("total_size") if isinstance(raw.get("metadata"), dict) else None
+    if total is not None and (isinstance(total, bool) or not isinstance(total, (int, float)) or total < 0 or total != int(total)):
+        raise SafetensorsError(f"{path}: metadata.total_size must be a non-negative integer, found {total!r}")
+    return out, (None if total is None else int(total))
+
+
 def open_model_files(model_dir) -> Tuple[Dict[str, TensorEntry], List[SafetensorsFile]]:
-    """All tensors of a folder's `*.safetensors` files (or of one file), by name."""
+    """All tensors of a folder's `*.safetensors` files (or of one file), by name.  With an index file in the
+    folder, the shards are those it names and every tensor must lie where it says: a shard that the index does
+    not know, a tensor that the index does not know or places elsewhere, an indexed tensor that no shard holds, or
+    a total size that differs from the shards' payload is an error (crates/mach-model/src/loader.rs:390-502)."""
     p = Path(model_dir)
-    paths = [p] if p.is_file() else sorted(p.glob("*.safetensors"))
+    index, total_size = (None if p.is_file() else read_shard_index(p)) or (None, None)
+    if index is not None:
+        named = sorted(set(index.values()))
+        stray = sorted(f.name for f in p.glob("*.safetensors") if f.name not in named)
+        if stray:
+            raise SafetensorsError(f"{p}: files that {INDEX_NAME} does not name: {', '.join(stray)}")
+        paths = [p / n for n in named]
+    else:
+        paths = [p] if p.is_file() else sorted(p.glob("*.safetensors"))
     if not paths:
         raise SafetensorsError(f"{p}: no *.safetensors file found")
     files, entries = [], {}
-    for path in paths:
-        f = SafetensorsFile(path)
-        files.append(f)
-        for name, e in f.entries.items():
-            if name in entries:
-                raise SafetensorsError(f"tensor '{name}' is in both {entries[name].file.path.name} and {path.name}")
-            entries[name] = e
+    try:
+        for path in paths:
+            f = SafetensorsFile(path)
+            files.append(f)
+            for name, e in f.entries.items():
+                if name in entries:
+                    raise SafetensorsError(f"tensor '{name}' is in both {entries[name].file.path.name} and {path.name}")
+                if index is not None and index.get(name) != path.name:
+                    where = f"is indexed in {index[name]}" if name in index else "is absent from the index"
+                    raise SafetensorsError(f"{path.name}: tensor '{name}' {where}")
+                entries[name] = e
+        if index is not None:
+            lost = sorted(n for n in index if n not in entries)
+            if lost:
+                raise SafetensorsError(f"{p / INDEX_NAME}: indexed tensors that no shard holds: {', '.join(lost[:8])}")
+            payload = sum(e.end - e.begin for e in entries.values())
+            if total_size is not None and payload != total_size:
+                raise SafetensorsError(f"{p / INDEX_NAME}: metadata.total_size is {total_size}, the shards hold {payload} bytes")
+    except SafetensorsError:
+        for f in files:
+            f.close()
+        raise
     return entries, files
 
 

@@ -85,3 +85,24 @@ def test_run_order_is_checked():
 def test_missing_config_file(tmp_path):
     with pytest.raises(ConfigError, match="no such file"):
         load_config(tmp_path)
+
+
+def test_memory_estimate_before_allocation():
+    """Weights once (a tied head costs nothing), pages of every layer, and the margin: the 0.5B sizes by hand."""
+    import torch
+
+    from machserve_b200.engine.runner import SCRATCH_MARGIN_BYTES, estimate_device_bytes
+    from machserve_b200.parts import DecoderModel
+
+    raw = {"architectures": ["Qwen2ForCausalLM"], "vocab_size": 151936, "hidden_size": 896, "num_hidden_layers": 24,
+           "num_attention_heads": 14, "num_key_value_heads": 2, "intermediate_size": 4864, "tie_word_embeddings": True}
+    model = DecoderModel(config_from_json(raw).model_spec())
+    est = estimate_device_bytes(model, torch.bfloat16, page_size=64, num_pages=100, max_requests=8, max_seq_len=2048)
+    d, i, qkv = 896, 4864, 896 + 2 * 128
+    per_layer = 2 * (d * qkv + d * d + 3 * d * i) + 4 * (qkv + 2 * d)
+    assert est["weights_bytes"] == 24 * per_layer + 2 * 151936 * d + 4 * d
+    assert est["cache_bytes"] == 24 * 100 * 64 * (2 * 2 * 64) * 2
+    assert est["table_bytes"] == 8 * 32 * 4 and est["state_bytes"] == 0
+    assert est["total_bytes"] == est["weights_bytes"] + est["cache_bytes"] + est["table_bytes"] + SCRATCH_MARGIN_BYTES
+    wide = estimate_device_bytes(model, torch.float32, page_size=64, num_pages=100, max_requests=8, max_seq_len=2048)
+    assert wide["cache_bytes"] == 2 * est["cache_bytes"]

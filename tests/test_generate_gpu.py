@@ -247,3 +247,10 @@ def test_random_load_running_ahead_equals_step_by_step(model_root, seed):
         assert tokens == plain and reason == ("stop" if eos is not None and plain[-1] == eos else "length")
         checked += 1
     assert checked >= 3
+
+
+def test_a_pool_that_cannot_fit_is_refused_with_the_numbers(model_root):
+    """The memory plan is compared with the device's free memory before anything is allocated."""
+    d = make_model_dir(model_root, "A")
+    with pytest.raises(RuntimeError, match="does not fit.*GiB are free"):
+        _engine(d, num_pages=1 << 30)

@@ -23,7 +23,8 @@ def test_round_trip_keeps_storage_dtypes(tmp_path):
     }
     write_safetensors(tmp_path / "model.safetensors", t)
     decls = [TensorDecl("a", (2, 3)), TensorDecl("b", (2,)), TensorDecl("h", (2,)), TensorDecl("i", (2, 2), init="table")]
-    kept = load_weights(tmp_path, decls, torch.bfloat16)
+    with pytest.warns(UserWarning, match="float16 and are rounded to bfloat16"):
+        kept = load_weights(tmp_path, decls, torch.bfloat16)
     # stored in 32 bits stays float32; 16-bit floats are kept as bfloat16; integer tables are int32
     assert kept["a"].dtype == torch.float32 and torch.equal(kept["a"], t["a"])
     assert kept["b"].dtype == torch.bfloat16 and torch.equal(kept["b"], t["b"])
@@ -114,6 +115,47 @@ def test_shards_are_read_together(tmp_path):
     write_safetensors(tmp_path / "model-00003.safetensors", {"a": torch.ones(2)})
     with pytest.raises(SafetensorsError, match="both"):
         open_model_files(tmp_path)
+
+
+def test_shard_index_is_honoured_and_checked(tmp_path):
+    """model.safetensors.index.json, when present, says which shards belong to the model and where each tensor lies."""
+    decls = [TensorDecl("a", (2,)), TensorDecl("b", (3,))]
+
+    def index(weight_map, **meta):
+        (tmp_path / "model.safetensors.index.json").write_text(json.dumps({"metadata": meta, "weight_map": weight_map}))
+
+    write_safetensors(tmp_path / "s1.safetensors", {"a": torch.ones(2)})
+    write_safetensors(tmp_path / "s2.safetensors", {"b": torch.zeros(3)})
+    index({"a": "s1.safetensors", "b": "s2.safetensors"}, total_size=20)
+    got = load_weights(tmp_path, decls, torch.float32)
+    assert got["a"].tolist() == [1, 1] and got["b"].tolist() == [0, 0, 0]
+    index({"a": "s1.safetensors", "b": "s2.safetensors"}, total_size=24)
+    with pytest.raises(SafetensorsError, match="total_size is 24, the shards hold 20"):
+        open_model_files(tmp_path)
+    index({"a": "s2.safetensors", "b": "s2.safetensors"})
+    with pytest.raises(SafetensorsError, match="does not name: s1.safetensors"):
+        open_model_files(tmp_path)
+    index({"a": "s1.safetensors", "b": "s1.safetensors", "c": "s2.safetensors"})
+    with pytest.raises(SafetensorsError, match="tensor 'b' is indexed in s1.safetensors"):
+        open_model_files(tmp_path)
+    index({"a": "s1.safetensors"})
+    with pytest.raises(SafetensorsError, match="does not name: s2.safetensors"):
+        open_model_files(tmp_path)
+    index({"a": "s1.safetensors", "b": "s2.safetensors", "c": "s2.safetensors"})
+    with pytest.raises(SafetensorsError, match="no shard holds: c"):
+        open_model_files(tmp_path)
+    index({"a": "s1.safetensors", "b": "s3.safetensors"})
+    with pytest.raises(SafetensorsError, match="s3.safetensors that it names is missing"):
+        open_model_files(tmp_path)
+    for bad in ("../s1.safetensors", "/etc/passwd", "s1.bin", 7):
+        index({"a": bad, "b": "s2.safetensors"})
+        with pytest.raises(SafetensorsError, match="must name a .safetensors file of this folder"):
+            open_model_files(tmp_path)
+    (tmp_path / "model.safetensors.index.json").write_text("{\"weight_map\": 3}")
+    with pytest.raises(SafetensorsError, match="'weight_map' is missing"):
+        open_model_files(tmp_path)
+    # a single file is read on its own, whatever index lies beside it
+    assert set(open_model_files(tmp_path / "s1.safetensors")[0]) == {"a"}
 
 
 def test_random_weights_depend_on_seed_and_name_only(model_root, tmp_path):
