@@ -31,7 +31,8 @@
 
 #define ATC_ROWS 128
 #define ATC_KEYS 128
-#define ATC_THREADS 192
+#define ATC_THREADS 192       // one head per block: four softmax warps, a copying warp, an issuing warp
+#define ATC_PAIR_THREADS 320  // two heads per block: two groups of four softmax warps, a copying warp, an issuing warp
 #define ATC_WAIT_LIMIT (1 << 21)
 #define ATC_LOG2E 1.4426950408889634f
 
@@ -88,6 +89,15 @@ __device__ __forceinline__ void atc_mma(unsigned tmem, unsigned long long adesc,
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem),
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// The same with the first operand in tensor memory: 128 lanes (rows) by 8 columns of two packed bfloat16 each
+// per 16 steps of k.
+__device__ __forceinline__ void atc_mma_ts(unsigned tmem_d, unsigned tmem_a, unsigned long long bdesc, unsigned idesc,
+                                           unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void atc_commit(unsigned bar) {
@@ -158,16 +168,15 @@ __device__ __forceinline__ float atc_row_max(const unsigned (&r)[ATC_KEYS], int 
   }
   return fmaxf(fmaxf(a[0], a[1]), fmaxf(a[2], a[3]));
 }
-// The probabilities 2^(s*scale_log2 - mu) of one half of a row (keys 64*HALF .. 64*HALF+63) as bfloat16 into
-// that half's panel of the swizzled K-major tile of P (128 bytes per row and panel); their float32 sums are
-// added to sum2 (two pairs).
+// The probabilities 2^(s*scale_log2 - mu) of one half of a row (keys 64*HALF .. 64*HALF+63), rounded to bfloat16
+// and packed in pairs back into the registers of scores already used (r[i / 2] for keys i, i + 1), as they go to
+// tensor memory; their float32 sums are added to sum2 (two pairs).
 template <bool INSIDE, int HALF>
-__device__ __forceinline__ void atc_row_probs(const unsigned (&r)[ATC_KEYS], int rlo, int rhi, float scale_log2, float mu,
-                                              unsigned char* p_s, int row, unsigned long long (&sum2)[2]) {
+__device__ __forceinline__ void atc_row_probs(unsigned (&r)[ATC_KEYS], int rlo, int rhi, float scale_log2, float mu,
+                                              unsigned long long (&sum2)[2]) {
   const unsigned long long scale2 = atc_pack(scale_log2, scale_log2), nmu2 = atc_pack(-mu, -mu);
-  unsigned char* panel = p_s + HALF * (128 * 128) + row * 128;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {  // 16-byte chunks of 8 probabilities
+  for (int j = 0; j < 8; ++j) {  // 8 probabilities at a time
     float p[8];
 #pragma unroll
     for (int e = 0; e < 8; e += 2) {
@@ -178,34 +187,138 @@ __device__ __forceinline__ void atc_row_probs(const unsigned (&r)[ATC_KEYS], int
       p[e + 1] = (INSIDE || (i + 1 >= rlo && i + 1 <= rhi)) ? atc_exp2(x1) : 0.f;
       sum2[(e >> 1) & 1] = atc_add2(sum2[(e >> 1) & 1], atc_pack(p[e], p[e + 1]));
     }
-    uint4 u;
-    __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&u);
+    const int w = (HALF * 64 + j * 8) >> 1;
 #pragma unroll
-    for (int e = 0; e < 4; ++e) hh[e] = __floats2bfloat162_rn(p[2 * e], p[2 * e + 1]);
-    *reinterpret_cast<uint4*>(panel + ((j ^ (row & 7)) << 4)) = u;
+    for (int e = 0; e < 4; ++e) {
+      __nv_bfloat162 h2 = __floats2bfloat162_rn(p[2 * e], p[2 * e + 1]);
+      r[w + e] = *reinterpret_cast<unsigned*>(&h2);
+    }
   }
 }
 
+
+#define ATC_MAX_SPLITS 4
+// What a split of an item (a tile of rows with one head) leaves in scratch memory: HD columns of O, then the
+// reference of the exponents m and the sum l, each as 128 consecutive rows.
+#define ATC_SPLIT_WORDS(HD) (((HD) + 2) * ATC_ROWS)
+
+// The end of a block's key tiles for the 128 rows of one head (one thread per row; the four warps of a softmax
+// group call it together).  With one split, out = O / l.  When the item's keys are split over several blocks, the
+// block leaves (O, m, l) in scratch memory and counts itself; the block that counts last merges all splits in
+// split order (so the result does not depend on who came last), writes the output and clears the counter.
+// No block waits for another.
+template <int HD>
+__device__ __forceinline__ void atc_finish(unsigned tmem_o_lane, bool have_o, float m, float l, int row, int nrows,
+                                           __nv_bfloat16* dst, int nsplit, int split, float* item_scratch, int* counter,
+                                           int bar_id, volatile int* last_flag) {
+  if (nsplit <= 1) {
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+    for (int c = 0; c < HD; c += 32) {
+      unsigned v[32];
+      if (have_o) {
+        atc_ld32_issue(tmem_o_lane + c, v);
+        atc_wait_ld();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = 0u;
+      }
+      if (row < nrows) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 u;
+          __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            hh[e] = __floats2bfloat162_rn(__uint_as_float(v[j * 8 + 2 * e]) * inv, __uint_as_float(v[j * 8 + 2 * e + 1]) * inv);
+          *reinterpret_cast<uint4*>(dst + c + j * 8) = u;
+        }
+      }
+    }
+    return;
+  }
+  float* mine = item_scratch + (size_t)split * ATC_SPLIT_WORDS(HD);
+#pragma unroll
+  for (int c = 0; c < HD; c += 32) {
+    unsigned v[32];
+    if (have_o) {
+      atc_ld32_issue(tmem_o_lane + c, v);
+      atc_wait_ld();
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = 0u;
+    }
+#pragma unroll
+    for (int i = 0; i < 32; ++i) __stcg(mine + (size_t)(c + i) * ATC_ROWS + row, __uint_as_float(v[i]));
+  }
+  __stcg(mine + (size_t)HD * ATC_ROWS + row, m);
+  __stcg(mine + (size_t)(HD + 1) * ATC_ROWS + row, l);
+  __threadfence();
+  asm volatile("bar.sync %0, 128;\n" ::"r"(bar_id) : "memory");
+  if (row == 0) *last_flag = atomicAdd(counter, 1) == nsplit - 1;
+  asm volatile("bar.sync %0, 128;\n" ::"r"(bar_id) : "memory");
+  if (!*last_flag) return;
+  __threadfence();
+  float ms[ATC_MAX_SPLITS], w[ATC_MAX_SPLITS];
+  float top = -INFINITY;
+#pragma unroll
+  for (int s = 0; s < ATC_MAX_SPLITS; ++s) {
+    ms[s] = s < nsplit ? __ldcg(item_scratch + (size_t)s * ATC_SPLIT_WORDS(HD) + (size_t)HD * ATC_ROWS + row) : -INFINITY;
+    top = fmaxf(top, ms[s]);
+  }
+  float sum = 0.f;
+#pragma unroll
+  for (int s = 0; s < ATC_MAX_SPLITS; ++s) {
+    const float ls = s < nsplit ? __ldcg(item_scratch + (size_t)s * ATC_SPLIT_WORDS(HD) + (size_t)(HD + 1) * ATC_ROWS + row) : 0.f;
+    w[s] = ls > 0.f ? atc_exp2(ms[s] - top) : 0.f;
+    sum += ls * w[s];
+  }
+  const float inv = sum > 0.f ? 1.f / sum : 0.f;
+  if (row < nrows) {
+#pragma unroll 1
+    for (int c = 0; c < HD; c += 8) {
+      float o[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = 0.f;
+#pragma unroll
+      for (int s = 0; s < ATC_MAX_SPLITS; ++s)
+        if (s < nsplit) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            o[e] += w[s] * __ldcg(item_scratch + (size_t)s * ATC_SPLIT_WORDS(HD) + (size_t)(c + e) * ATC_ROWS + row);
+        }
+      uint4 u;
+      __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) hh[e] = __floats2bfloat162_rn(o[2 * e] * inv, o[2 * e + 1] * inv);
+      *reinterpret_cast<uint4*>(dst + c) = u;
+    }
+  }
+  if (row == 0) *counter = 0;
+}
 
 struct AtcShared {
   unsigned long long q_full, k_full, k_empty, v_full[2], v_empty[2], s_full, s_free, p_full, o_full;
   unsigned tmem_base;
   int abort_flag;
+  int last_flag;
+  volatile int group_bad;
 };
 
-// Shared memory: [AtcShared, 1 KB][Q: HD/64 panels of 16 KB][V stage 0, 1][K][P: 2 panels of 16 KB]; a panel
-// is 128 rows of 128 bytes.  Keys have one stage (the next tile's keys are copied while the softmax of this
-// one runs), values two.  With head size 64 that is 98 KB, so two blocks share an SM and one's softmax
-// overlaps the other's.  The value tiles are not last: the tensor core's fetch of an MN-major operand was
+// One head per block, for head size 64.  Shared memory: [AtcShared, 1 KB][Q: a panel of 16 KB][V stage 0, 1][K]; a
+// panel is 128 rows of 128 bytes.  Keys have one stage (the next tile's keys are copied while the softmax of this
+// one runs), values two.  That is 66 KB and 256 columns of tensor memory (S 128, O 64, P 64 as packed pairs), so two
+// blocks share an SM and one's softmax overlaps the other's.  The value tiles are not last: the tensor core's fetch of an MN-major operand was
 // seen to reach past the tile it is given.
 template <int HD>
 __global__ void __launch_bounds__(ATC_THREADS, 2)
-attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+attention_prefill_tc_single_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                             const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
                             const int* __restrict__ positions, const int* __restrict__ slot_of_token,
                             const int* __restrict__ block_table, int max_pages, int num_pages, int hq, int hkv,
-                            int page_size, int window, float scale_log2) {
+                            int page_size, int window, float scale_log2, float* __restrict__ scratch,
+                            int* __restrict__ counters) {
   constexpr int PANELS = HD / 64;          // 64-column panels of Q, K and V
   constexpr int PANEL_BYTES = 128 * 128;   // 128 rows of 128 bytes
   constexpr int KV_BYTES = PANELS * PANEL_BYTES;
@@ -215,7 +328,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   unsigned char* q_s = base + 1024;
   unsigned char* v_s = q_s + KV_BYTES;       // two stages
   unsigned char* k_s = v_s + 2 * KV_BYTES;   // one stage
-  unsigned char* p_s = k_s + KV_BYTES;       // two panels
   volatile int* abort_flag = &sh->abort_flag;
 
   const int tile_id = gridDim.x - 1 - blockIdx.x;  // the longest tiles first
@@ -226,8 +338,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int pos0 = positions[row0];
   const int pos_last = pos0 + nrows - 1;
   const int first_key = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
-  const int tile_lo = first_key / ATC_KEYS, tile_hi = pos_last / ATC_KEYS;
-  const int ntiles = (slot >= 0 && nrows > 0) ? tile_hi - tile_lo + 1 : 0;
+  const int item_lo = first_key / ATC_KEYS, tile_hi = pos_last / ATC_KEYS;
+  const int item_tiles = (slot >= 0 && nrows > 0) ? tile_hi - item_lo + 1 : 0;
+  // the item's key tiles in gridDim.z runs of equal length; blocks past the last run have nothing to do
+  const int chunk = (item_tiles + (int)gridDim.z - 1) / (int)gridDim.z;
+  const int nsplit = chunk > 0 ? (item_tiles + chunk - 1) / chunk : 1;
+  const int split = blockIdx.z;
+  const bool active = split < nsplit;
+  const int tile_lo = item_lo + split * chunk;
+  const int ntiles = (active && chunk > 0) ? min(chunk, item_tiles - split * chunk) : 0;
   const int* table = block_table + (size_t)(slot >= 0 ? slot : 0) * max_pages;
 
   if (tid == 0) {
@@ -243,6 +362,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     atc_mbar_init(atc_smem(&sh->p_full), ATC_ROWS);
     atc_mbar_init(atc_smem(&sh->o_full), 1);
     sh->abort_flag = 0;
+    sh->group_bad = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   // the key and value stages start as zeros: rows that no page holds are never copied, and what multiplies a
@@ -258,7 +378,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   __syncthreads();
   atc_fence_after();
   const unsigned tmem = sh->tmem_base;
-  const unsigned tmem_s = tmem, tmem_o = tmem + 128;  // columns 0..127: S; 128..128+HD-1: O_t
+  const unsigned tmem_s = tmem, tmem_o = tmem + 128;  // columns 0..127: S; 128..128+HD-1: O
+  const unsigned tmem_p = tmem + 192;                 // 64 columns of packed bfloat16 P
 
   if (warp == 4 && lane == 0) {
     // ------------------------------------------------------------------ producer
@@ -315,7 +436,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const unsigned idesc_s = atc_idesc(ATC_ROWS, ATC_KEYS, false);
     const unsigned idesc_o = atc_idesc(ATC_ROWS, 64, true);
     // the descriptors once; an offset of b bytes inside a tile adds b / 16 to the address field
-    const unsigned long long desc_q = atc_desc(atc_smem(q_s)), desc_k = atc_desc(atc_smem(k_s)), desc_p = atc_desc(atc_smem(p_s));
+    const unsigned long long desc_q = atc_desc(atc_smem(q_s)), desc_k = atc_desc(atc_smem(k_s));
     const unsigned long long desc_v0 = atc_desc(atc_smem(v_s)), desc_v1 = atc_desc(atc_smem(v_s + KV_BYTES));
     // O += P V of tile j over its 128 keys in steps of 16; one instruction per 64 columns of hd
     auto issue_pv = [&](int j) -> bool {
@@ -327,11 +448,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       atc_fence_after();
 #pragma unroll
       for (int k = 0; k < ATC_KEYS / 16; ++k) {
-        const unsigned a_off = (k >> 2) * PANEL_BYTES + (k & 3) * 32;
 #pragma unroll
         for (int p = 0; p < PANELS; ++p)
-          atc_mma(tmem_o + p * 64, desc_p + (a_off >> 4), desc_v + ((p * PANEL_BYTES + k * 2048) >> 4), idesc_o,
-                  (j > 0 || k != 0) ? 1u : 0u);
+          atc_mma_ts(tmem_o + p * 64, tmem_p + k * 8, desc_v + ((p * PANEL_BYTES + k * 2048) >> 4), idesc_o,
+                     (j > 0 || k != 0) ? 1u : 0u);  // 16 keys = 8 columns of packed pairs
       }
       atc_commit(atc_smem(&sh->v_empty[s]));
       atc_commit(atc_smem(&sh->o_full));
@@ -396,11 +516,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       unsigned long long sum2[2] = {atc_pack(0.f, 0.f), atc_pack(0.f, 0.f)};
       if (inside) {
-        atc_row_probs<true, 0>(r, rlo, rhi, scale_log2, mu, p_s, row, sum2);
-        atc_row_probs<true, 1>(r, rlo, rhi, scale_log2, mu, p_s, row, sum2);
+        atc_row_probs<true, 0>(r, rlo, rhi, scale_log2, mu, sum2);
+        atc_row_probs<true, 1>(r, rlo, rhi, scale_log2, mu, sum2);
       } else {
-        atc_row_probs<false, 0>(r, rlo, rhi, scale_log2, mu, p_s, row, sum2);
-        atc_row_probs<false, 1>(r, rlo, rhi, scale_log2, mu, p_s, row, sum2);
+        atc_row_probs<false, 0>(r, rlo, rhi, scale_log2, mu, sum2);
+        atc_row_probs<false, 1>(r, rlo, rhi, scale_log2, mu, sum2);
       }
       float s0, s1, s2, s3;
       atc_unpack(sum2[0], s0, s1);
@@ -418,38 +538,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
         atc_fence_before();
       }
-      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the tensor core reads P through the async proxy
+      atc_st32(tmem_p + lane_addr, r);  // the row of P, two bfloat16 to a column
+      atc_st32(tmem_p + lane_addr + 32, r + 32);
+      atc_fence_before();
       atc_mbar_arrive(atc_smem(&sh->p_full));
     }
     if (ok && ntiles > 0) {
       ok = atc_mbar_wait(atc_smem(&sh->o_full), (ntiles - 1) & 1, abort_flag, 15);
       atc_fence_after();
     }
-    if (__all_sync(0xffffffffu, ok)) {
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* dst = out + ((size_t)(row0 + row) * hq + h) * HD;
-#pragma unroll
-      for (int c = 0; c < HD; c += 32) {
-        unsigned v[32];
-        if (ntiles > 0) {
-          atc_ld32_issue(tmem_o + lane_addr + c, v);
-          atc_wait_ld();
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = 0u;
-        }
-        if (row < nrows) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint4 u;
-            __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&u);
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-              hh[e] = __floats2bfloat162_rn(__uint_as_float(v[j * 8 + 2 * e]) * inv, __uint_as_float(v[j * 8 + 2 * e + 1]) * inv);
-            *reinterpret_cast<uint4*>(dst + c + j * 8) = u;
-          }
-        }
-      }
+    // whether the whole group got through: decided behind a barrier that all of its 128 threads reach whatever
+    // happened, so that the barriers inside atc_finish are reached by all of them or by none
+    if (!ok) sh->group_bad = 1;
+    asm volatile("bar.sync 1, 128;\n" ::: "memory");
+    if (!sh->group_bad && active) {
+      const size_t item = (size_t)tile_id * hq + h;
+      atc_finish<HD>(tmem_o + lane_addr, ntiles > 0, m, l, row, nrows, out + ((size_t)(row0 + row) * hq + h) * HD, nsplit, split,
+                     scratch + item * gridDim.z * ATC_SPLIT_WORDS(HD), counters + item, 1, &sh->last_flag);
       atc_fence_before();
     }
   }
@@ -460,6 +565,299 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     __syncthreads();
   }
   if (warp == 5) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(256) : "memory");
+}
+
+
+struct AtcPairShared {
+  unsigned long long q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], o_done;
+  unsigned tmem_base;
+  int abort_flag;
+  int last_flag[2];
+  volatile int group_bad[2];
+};
+
+// Shared memory: [AtcShared, 1 KB][Q of head A][Q of head B][V stage 0, 1][K stage 0, 1]; a tile is HD/64 panels
+// of 128 rows of 128 bytes.  The value tiles are not last: the tensor core's fetch of an MN-major operand was
+// seen to reach past the tile it is given.  Tensor memory (all 512 columns, so one block per SM): S of head A
+// in columns 0..127, S of head B in 128..255, O of head A from 256, O of head B from 384; the probabilities of a
+// head, packed two bfloat16 to a column, take the place of the first 64 columns of its scores.
+template <int HD>
+__global__ void __launch_bounds__(ATC_PAIR_THREADS, 1)
+attention_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
+                            const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
+                            const int* __restrict__ positions, const int* __restrict__ slot_of_token,
+                            const int* __restrict__ block_table, int max_pages, int num_pages, int hq, int hkv,
+                            int page_size, int window, float scale_log2, float* __restrict__ scratch,
+                            int* __restrict__ counters) {
+  constexpr int PANELS = HD / 64;          // 64-column panels of Q, K and V
+  constexpr int PANEL_BYTES = 128 * 128;   // 128 rows of 128 bytes
+  constexpr int KV_BYTES = PANELS * PANEL_BYTES;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  AtcPairShared* sh = reinterpret_cast<AtcPairShared*>(base);
+  unsigned char* q_s = base + 1024;          // head A, head B
+  unsigned char* v_s = q_s + 2 * KV_BYTES;   // two stages
+  unsigned char* k_s = v_s + 2 * KV_BYTES;   // two stages
+  volatile int* abort_flag = &sh->abort_flag;
+
+  const int tile_id = gridDim.x - 1 - blockIdx.x;  // the longest tiles first
+  const int row0 = tile_row0[tile_id], nrows = tile_rows[tile_id];
+  const int groups = hq / hkv, pairs = (groups + 1) >> 1;
+  const int kvh = blockIdx.y / pairs, pair = blockIdx.y - kvh * pairs;
+  const int head_a = kvh * groups + 2 * pair;
+  const bool has_b = 2 * pair + 1 < groups;  // a group of an odd number of heads leaves its last head alone
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int slot = slot_of_token[row0];
+  const int pos0 = positions[row0];
+  const int pos_last = pos0 + nrows - 1;
+  const int first_key = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+  const int item_lo = first_key / ATC_KEYS, tile_hi = pos_last / ATC_KEYS;
+  const int item_tiles = (slot >= 0 && nrows > 0) ? tile_hi - item_lo + 1 : 0;
+  // the item's key tiles in gridDim.z runs of equal length; blocks past the last run have nothing to do
+  const int chunk = (item_tiles + (int)gridDim.z - 1) / (int)gridDim.z;
+  const int nsplit = chunk > 0 ? (item_tiles + chunk - 1) / chunk : 1;
+  const int split = blockIdx.z;
+  const bool active = split < nsplit;
+  const int tile_lo = item_lo + split * chunk;
+  const int ntiles = (active && chunk > 0) ? min(chunk, item_tiles - split * chunk) : 0;
+  const int* table = block_table + (size_t)(slot >= 0 ? slot : 0) * max_pages;
+
+  if (tid == 0) {
+    atc_mbar_init(atc_smem(&sh->q_full), 1);
+    for (int s = 0; s < 2; ++s) {
+      atc_mbar_init(atc_smem(&sh->k_full[s]), 1);
+      atc_mbar_init(atc_smem(&sh->k_empty[s]), 1);
+      atc_mbar_init(atc_smem(&sh->v_full[s]), 1);
+      atc_mbar_init(atc_smem(&sh->v_empty[s]), 1);
+      atc_mbar_init(atc_smem(&sh->s_full[s]), 1);
+      atc_mbar_init(atc_smem(&sh->p_full[s]), ATC_ROWS);
+    }
+    atc_mbar_init(atc_smem(&sh->o_done), 1);
+    sh->abort_flag = 0;
+    sh->group_bad[0] = sh->group_bad[1] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  // the key and value stages start as zeros: rows that no page holds are never copied, and what multiplies a
+  // probability of zero must be finite
+  for (int i = tid; i < 4 * KV_BYTES / 16; i += ATC_PAIR_THREADS) reinterpret_cast<uint4*>(v_s)[i] = make_uint4(0, 0, 0, 0);
+  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  if (warp == 9) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(atc_smem(&sh->tmem_base)), "r"(512)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  atc_fence_before();
+  __syncthreads();
+  atc_fence_after();
+  const unsigned tmem = sh->tmem_base;
+
+  if (warp == 8 && lane == 0) {
+    // ------------------------------------------------------------------ producer
+    if (ntiles > 0) {
+      atc_mbar_expect_tx(atc_smem(&sh->q_full), (has_b ? 2 : 1) * KV_BYTES);
+      for (int x = 0; x < (has_b ? 2 : 1); ++x)
+        for (int p = 0; p < PANELS; ++p)
+          atc_tma_2d(atc_smem(q_s + x * KV_BYTES + p * PANEL_BYTES), &map_q, (head_a + x) * HD + p * 64, row0, atc_smem(&sh->q_full));
+    }
+    // One thread does all of this next to the softmax warps, so every instruction counts: the page size is a
+    // power of two (shifts and masks, no division), and the keys go out before anything else is looked at.
+    const int box = page_size < ATC_KEYS ? page_size : ATC_KEYS;  // rows one copy brings
+    const int page_shift = __ffs(page_size) - 1, page_mask = page_size - 1;
+    const unsigned copy_bytes = (unsigned)PANELS * box * 128;
+    for (int t = 0; t < ntiles; ++t) {
+      const int s = t & 1;
+      const int key0 = (tile_lo + t) * ATC_KEYS;
+      // which copies will be made: pages the table holds, inside the keys the tile's rows can see
+      unsigned bytes = 0;
+      for (int r = 0; r < ATC_KEYS; r += box) {
+        const int key = key0 + r;
+        if (key > pos_last || key + box - 1 < first_key) continue;
+        const int page = table[key >> page_shift];
+        if (page >= 0 && page < num_pages) bytes += copy_bytes;
+      }
+      // keys first: the scores of tile t are wanted a whole tile before its values are
+      if (t >= 2 && !atc_mbar_wait(atc_smem(&sh->k_empty[s]), ((t >> 1) - 1) & 1, abort_flag, 11)) break;
+      atc_mbar_expect_tx(atc_smem(&sh->k_full[s]), bytes);
+      for (int r = 0; r < ATC_KEYS; r += box) {
+        const int key = key0 + r;
+        if (key > pos_last || key + box - 1 < first_key) continue;
+        const int page = table[key >> page_shift];
+        if (page < 0 || page >= num_pages) continue;
+        const int grow = (page * hkv + kvh) * page_size + (key & page_mask);  // row of the [pages*kv_heads*page, hd] view
+#pragma unroll
+        for (int p = 0; p < PANELS; ++p)
+          atc_tma_2d(atc_smem(k_s + s * KV_BYTES + p * PANEL_BYTES + r * 128), &map_k, p * 64, grow, atc_smem(&sh->k_full[s]));
+      }
+      if (t >= 2 && !atc_mbar_wait(atc_smem(&sh->v_empty[s]), ((t >> 1) - 1) & 1, abort_flag, 11)) break;
+      atc_mbar_expect_tx(atc_smem(&sh->v_full[s]), bytes);
+      for (int r = 0; r < ATC_KEYS; r += box) {
+        const int key = key0 + r;
+        if (key > pos_last || key + box - 1 < first_key) continue;
+        const int page = table[key >> page_shift];
+        if (page < 0 || page >= num_pages) continue;
+        const int grow = (page * hkv + kvh) * page_size + (key & page_mask);
+#pragma unroll
+        for (int p = 0; p < PANELS; ++p)
+          atc_tma_2d(atc_smem(v_s + s * KV_BYTES + p * PANEL_BYTES + r * 128), &map_v, p * 64, grow, atc_smem(&sh->v_full[s]));
+      }
+    }
+  } else if (warp == 9 && lane == 0) {
+    // -------------------------------------------------------------------- issuer
+    // The tensor core works through its instructions in the order they are issued, and a commit arrives when
+    // everything issued before it is done.  Per key tile t: P V of head A (when its probabilities are written),
+    // then the scores of head A for tile t + 1 (which overwrite those probabilities: P V was issued first, so it
+    // has read them), then the same for head B.  While one head's softmax runs, the other head's products do.
+    bool ok = ntiles == 0 || atc_mbar_wait(atc_smem(&sh->q_full), 0, abort_flag, 12);
+    const unsigned idesc_s = atc_idesc(ATC_ROWS, ATC_KEYS, false);
+    const unsigned idesc_o = atc_idesc(ATC_ROWS, 64, true);
+    // the descriptors once; an offset of b bytes inside a tile adds b / 16 to the address field
+    const unsigned long long desc_q0 = atc_desc(atc_smem(q_s)), desc_q1 = atc_desc(atc_smem(q_s + KV_BYTES));
+    const unsigned long long desc_k0 = atc_desc(atc_smem(k_s)), desc_k1 = atc_desc(atc_smem(k_s + KV_BYTES));
+    const unsigned long long desc_v0 = atc_desc(atc_smem(v_s)), desc_v1 = atc_desc(atc_smem(v_s + KV_BYTES));
+    // S = Q K^T over hd in steps of 16 (four steps per 64-column panel)
+    auto issue_qk = [&](int x, int s) {
+      const unsigned long long dq = x ? desc_q1 : desc_q0, dk = s ? desc_k1 : desc_k0;
+#pragma unroll
+      for (int k = 0; k < HD / 16; ++k) {
+        const unsigned off = (k >> 2) * PANEL_BYTES + (k & 3) * 32;
+        atc_mma(tmem + x * 128, dq + (off >> 4), dk + (off >> 4), idesc_s, k != 0);
+      }
+      atc_commit(atc_smem(&sh->s_full[x]));
+    };
+    // O += P V over the tile's 128 keys in steps of 16 (8 columns of packed pairs); one instruction per 64 columns of hd
+    auto issue_pv = [&](int x, int s, int t) {
+      const unsigned long long dv = s ? desc_v1 : desc_v0;
+#pragma unroll
+      for (int k = 0; k < ATC_KEYS / 16; ++k)
+#pragma unroll
+        for (int p = 0; p < PANELS; ++p)
+          atc_mma_ts(tmem + 256 + x * 128 + p * 64, tmem + x * 128 + k * 8, dv + ((p * PANEL_BYTES + k * 2048) >> 4), idesc_o,
+                     (t > 0 || k != 0) ? 1u : 0u);
+    };
+    if (ok && ntiles > 0) {
+      ok = atc_mbar_wait(atc_smem(&sh->k_full[0]), 0, abort_flag, 13);
+      if (ok) {
+        atc_fence_after();
+        issue_qk(0, 0);
+        if (has_b) issue_qk(1, 0);
+        atc_commit(atc_smem(&sh->k_empty[0]));
+      }
+    }
+    for (int t = 0; t < ntiles && ok; ++t) {
+      const int s = t & 1, s1 = s ^ 1;
+      const bool next = t + 1 < ntiles;
+      ok = atc_mbar_wait(atc_smem(&sh->p_full[0]), t & 1, abort_flag, 14) &&
+           atc_mbar_wait(atc_smem(&sh->v_full[s]), (t >> 1) & 1, abort_flag, 14);
+      if (!ok) break;
+      atc_fence_after();
+      issue_pv(0, s, t);
+      if (!has_b) atc_commit(atc_smem(&sh->v_empty[s]));
+      if (next) {
+        ok = atc_mbar_wait(atc_smem(&sh->k_full[s1]), ((t + 1) >> 1) & 1, abort_flag, 13);
+        if (!ok) break;
+        atc_fence_after();
+        issue_qk(0, s1);
+        if (!has_b) atc_commit(atc_smem(&sh->k_empty[s1]));
+      }
+      if (has_b) {
+        ok = atc_mbar_wait(atc_smem(&sh->p_full[1]), t & 1, abort_flag, 16);
+        if (!ok) break;
+        atc_fence_after();
+        issue_pv(1, s, t);
+        atc_commit(atc_smem(&sh->v_empty[s]));
+        if (next) {
+          issue_qk(1, s1);
+          atc_commit(atc_smem(&sh->k_empty[s1]));
+        }
+      }
+    }
+    if (ok && ntiles > 0) atc_commit(atc_smem(&sh->o_done));
+  } else if (warp < 8) {
+    // ------------------------------------------------------------ softmax threads
+    const int x = warp >> 2;      // which head of the pair
+    const int row = tid & 127;    // accumulator lane = query row of the tile
+    const int pos = pos0 + row;
+    const int hi = row < nrows ? pos : -1;
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const unsigned lane_addr = (unsigned)((warp & 3) * 32) << 16;
+    const unsigned tmem_s = tmem + x * 128, tmem_o = tmem + 256 + x * 128;
+    const int steps = (x == 0 || has_b) ? ntiles : 0;
+    float m = -INFINITY, l = 0.f;  // the reference of the row's exponents, the sum of its probabilities
+    bool ok = true;
+    for (int t = 0; t < steps && ok; ++t) {
+      ok = atc_mbar_wait(atc_smem(&sh->s_full[x]), t & 1, abort_flag, 15);
+      if (!ok) break;
+      atc_fence_after();
+      // the scores have arrived, and with them (the tensor core works in order) the product P V of the tile before
+      unsigned r[ATC_KEYS];
+#pragma unroll
+      for (int c = 0; c < ATC_KEYS; c += 32) atc_ld32_issue(tmem_s + lane_addr + c, r + c);
+      atc_wait_ld();
+      const int key0 = (tile_lo + t) * ATC_KEYS;
+      const int rlo = lo - key0, rhi = hi - key0;
+      // whether every row of this warp sees the whole tile: the same for the whole warp, which keeps the
+      // warp-wide tensor memory instructions below out of divergent code
+      const bool inside = __all_sync(0xffffffffu, rlo <= 0 && rhi >= ATC_KEYS - 1);
+      const float mx = (inside ? atc_row_max<true>(r, rlo, rhi) : atc_row_max<false>(r, rlo, rhi)) * scale_log2;
+      // the reference moves only when the maximum has grown by more than 8; a row that has seen no key yet
+      // (m = -inf) has nothing in O to rescale
+      const bool grow = mx > m + 8.f;
+      const float corr = grow ? atc_exp2(m - mx) : 1.f;
+      const bool rescale = __any_sync(0xffffffffu, grow && m != -INFINITY);
+      m = grow ? mx : m;
+      const float mu = m == -INFINITY ? 0.f : m;
+      unsigned long long sum2[2] = {atc_pack(0.f, 0.f), atc_pack(0.f, 0.f)};
+      if (inside) {
+        atc_row_probs<true, 0>(r, rlo, rhi, scale_log2, mu, sum2);
+        atc_row_probs<true, 1>(r, rlo, rhi, scale_log2, mu, sum2);
+      } else {
+        atc_row_probs<false, 0>(r, rlo, rhi, scale_log2, mu, sum2);
+        atc_row_probs<false, 1>(r, rlo, rhi, scale_log2, mu, sum2);
+      }
+      float s0, s1, s2, s3;
+      atc_unpack(sum2[0], s0, s1);
+      atc_unpack(sum2[1], s2, s3);
+      l = l * corr + ((s0 + s1) + (s2 + s3));
+      if (rescale) {  // (now, when the row of scores has shrunk to 64 registers of packed pairs)
+#pragma unroll
+        for (int c = 0; c < HD; c += 32) {
+          unsigned v[32];
+          atc_ld32_issue(tmem_o + lane_addr + c, v);
+          atc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+          atc_st32(tmem_o + lane_addr + c, v);
+        }
+      }
+      // the row of P, two bfloat16 to a column, over the first 64 columns of the scores it was made from
+      atc_st32(tmem_s + lane_addr, r);
+      atc_st32(tmem_s + lane_addr + 32, r + 32);
+      atc_fence_before();
+      atc_mbar_arrive(atc_smem(&sh->p_full[x]));
+    }
+    if (ok && steps > 0) {
+      ok = atc_mbar_wait(atc_smem(&sh->o_done), 0, abort_flag, 15);
+      atc_fence_after();
+    }
+    // whether the whole group got through: decided behind a barrier that all of its 128 threads reach whatever
+    // happened, so that the barriers inside atc_finish are reached by all of them or by none
+    if (!ok) sh->group_bad[x] = 1;
+    asm volatile("bar.sync %0, 128;\n" ::"r"(1 + x) : "memory");
+    if (!sh->group_bad[x] && (x == 0 || has_b) && active) {
+      const size_t item = (size_t)tile_id * hq + head_a + x;
+      atc_finish<HD>(tmem_o + lane_addr, steps > 0, m, l, row, nrows, out + ((size_t)(row0 + row) * hq + head_a + x) * HD, nsplit,
+                     split, scratch + item * gridDim.z * ATC_SPLIT_WORDS(HD), counters + item, 1 + x, &sh->last_flag[x]);
+      atc_fence_before();
+    }
+  }
+  atc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 9) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512) : "memory");
 }
 
 // ------------------------------------------------------------------------------------ host
@@ -488,22 +886,47 @@ static int atc_make_map(CUtensorMap* map, const void* base, long long rows, int 
   return 0;
 }
 
-template <int HD>
-static int atc_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, const int* tile_row0,
-                      const int* tile_rows, int num_tiles, const int* positions, const int* slot_of_token,
-                      const int* block_table, int max_pages, int num_pages, int hq, int hkv, int page_size, int window,
-                      float scale, cudaStream_t stream) {
-  const size_t smem = 1024 + 1024 + (size_t)(HD / 64) * 16384 * 4 + 2 * 16384;
-  auto kern = attention_prefill_tc_kernel<HD>;
+static int atc_launch_single(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, const int* tile_row0,
+                             const int* tile_rows, int num_tiles, const int* positions, const int* slot_of_token,
+                             const int* block_table, int max_pages, int num_pages, int hq, int hkv, int page_size, int window,
+                             float scale, int splits, float* scratch, int* counters, cudaStream_t stream) {
+  const size_t smem = 1024 + 1024 + (size_t)16384 * 4;
+  auto kern = attention_prefill_tc_single_kernel<64>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     MS_REQUIRE(e == cudaSuccess, "attention_prefill_tc: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  dim3 grid(num_tiles, hq);
+  dim3 grid(num_tiles, hq, splits);
   kern<<<grid, ATC_THREADS, smem, stream>>>(mq, mk, mv, (__nv_bfloat16*)out, tile_row0, tile_rows, positions, slot_of_token,
-                                            block_table, max_pages, num_pages, hq, hkv, page_size, window, scale * ATC_LOG2E);
+                                            block_table, max_pages, num_pages, hq, hkv, page_size, window, scale * ATC_LOG2E,
+                                            scratch, counters);
+  MS_LAUNCH_CHECK("attention_prefill_tc");
+  return 0;
+}
+
+template <int HD>
+static int atc_launch_pair(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, const int* tile_row0,
+                           const int* tile_rows, int num_tiles, const int* positions, const int* slot_of_token,
+                           const int* block_table, int max_pages, int num_pages, int hq, int hkv, int page_size, int window,
+                           float scale, int splits, float* scratch, int* counters, cudaStream_t stream) {
+  // two heads' Q, two stages of K and of V (194 KB at head size 128); never less than half an SM's shared memory, so
+  // that a block has the SM and all of its tensor memory to itself
+  size_t smem = 1024 + 1024 + (size_t)(HD / 64) * 16384 * 6;
+  if (smem < 120 * 1024) smem = 120 * 1024;
+  auto kern = attention_prefill_tc_pair_kernel<HD>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    MS_REQUIRE(e == cudaSuccess, "attention_prefill_tc: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  const int groups = hq / hkv;
+  dim3 grid(num_tiles, hkv * ((groups + 1) / 2), splits);  // a block attends a tile of rows with two heads of one group
+  kern<<<grid, ATC_PAIR_THREADS, smem, stream>>>(mq, mk, mv, (__nv_bfloat16*)out, tile_row0, tile_rows, positions, slot_of_token,
+                                                 block_table, max_pages, num_pages, hq, hkv, page_size, window, scale * ATC_LOG2E,
+                                                 scratch, counters);
   MS_LAUNCH_CHECK("attention_prefill_tc");
   return 0;
 }
@@ -544,16 +967,45 @@ MS_API int ms_attention_prefill_tc_supports(int hd, int page_size) {
   return (hd == 64 || hd == 128) && page_size >= 8 && (page_size & (page_size - 1)) == 0;
 }
 
-// As ms_attention_prefill, with tiles of up to 128 rows.  q, out: bfloat16 [total_rows, hq*hd].
+// float32 words of scratch memory that `splits` > 1 need: every item's partial results, then one counter per item
+// (which must be zero before the first launch and is left zero by every launch).
+MS_API long long ms_attention_prefill_tc_scratch_words(int num_tiles, int hq, int hd, int splits) {
+  if (splits <= 1) return 0;
+  return (long long)num_tiles * hq * splits * ATC_SPLIT_WORDS(hd) + (long long)num_tiles * hq;
+}
+
+// How many runs the key tiles of every item are cut into so that a launch fills the GPU: few tiles of rows (a short
+// prompt, a portion of a long one) would leave most SMs idle behind the blocks with the longest rows of key tiles.
+// `max_keys`: the most keys any row of the launch sees.
+MS_API int ms_attention_prefill_tc_splits(int num_tiles, int hq, int hkv, int hd, int max_keys, int sm_count) {
+  if (num_tiles <= 0 || hq <= 0 || hkv <= 0) return 1;
+  const int groups = hq / hkv;
+  const long long blocks = (long long)num_tiles * (hd == 64 ? hq : hkv * ((groups + 1) / 2));
+  const long long slots = (long long)sm_count * (hd == 64 ? 2 : 1);
+  int splits = (int)(slots / (blocks > 0 ? blocks : 1));
+  const int key_tiles = (max_keys + ATC_KEYS - 1) / ATC_KEYS;
+  if (splits > key_tiles / 4) splits = key_tiles / 4;  // at least four key tiles per run: a merge costs about one
+  if (splits > ATC_MAX_SPLITS) splits = ATC_MAX_SPLITS;
+  return splits < 1 ? 1 : splits;
+}
+
+// As ms_attention_prefill, with tiles of up to 128 rows.  q, out: bfloat16 [total_rows, hq*hd].  `splits` (1 to 4): the
+// key tiles of every item go to that many blocks, which meet in `scratch` (ms_attention_prefill_tc_scratch_words).
 MS_API int ms_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, void* out, int total_rows,
                                    const int* tile_row0, const int* tile_rows, int num_tiles, const int* positions,
                                    const int* slot_of_token, const int* block_table, int max_pages, int num_pages, int hq,
-                                   int hkv, int hd, int page_size, int window, float scale, cudaStream_t stream) {
+                                   int hkv, int hd, int page_size, int window, float scale, int splits, float* scratch,
+                                   long long scratch_words, cudaStream_t stream) {
   if (num_tiles == 0) return 0;
   MS_REQUIRE(num_tiles > 0 && total_rows > 0 && hq > 0 && hkv > 0 && hq % hkv == 0 && hq <= 65535, "attention_prefill_tc: bad sizes");
   MS_REQUIRE(ms_attention_prefill_tc_supports(hd, page_size),
              "attention_prefill_tc: head_dim %d (64 or 128) or page size %d (a power of two from 8) is not covered", hd, page_size);
   MS_REQUIRE(((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)out) % 16 == 0, "attention_prefill_tc: operands must be 16-byte aligned");
+  MS_REQUIRE(splits >= 1 && splits <= ATC_MAX_SPLITS, "attention_prefill_tc: %d splits (1 to %d)", splits, ATC_MAX_SPLITS);
+  const long long need = ms_attention_prefill_tc_scratch_words(num_tiles, hq, hd, splits);
+  MS_REQUIRE(need == 0 || (scratch != nullptr && scratch_words >= need),
+             "attention_prefill_tc: %d splits need %lld words of scratch memory, %lld were given", splits, need, scratch_words);
+  int* counters = need ? reinterpret_cast<int*>(scratch + (need - (long long)num_tiles * hq)) : nullptr;
   CUtensorMap mq, mk, mv;
   if (int rc = atc_make_map(&mq, q, total_rows, hq * hd, hq * hd, ATC_ROWS)) return rc;
   const int box = page_size < ATC_KEYS ? page_size : ATC_KEYS;
@@ -561,8 +1013,8 @@ MS_API int ms_attention_prefill_tc(const void* q, const void* k_pages, const voi
   if (int rc = atc_make_map(&mk, k_pages, cache_rows, hd, hd, box)) return rc;
   if (int rc = atc_make_map(&mv, v_pages, cache_rows, hd, hd, box)) return rc;
   if (hd == 64)
-    return atc_launch<64>(mq, mk, mv, out, tile_row0, tile_rows, num_tiles, positions, slot_of_token, block_table, max_pages,
-                          num_pages, hq, hkv, page_size, window, scale, stream);
-  return atc_launch<128>(mq, mk, mv, out, tile_row0, tile_rows, num_tiles, positions, slot_of_token, block_table, max_pages,
-                         num_pages, hq, hkv, page_size, window, scale, stream);
+    return atc_launch_single(mq, mk, mv, out, tile_row0, tile_rows, num_tiles, positions, slot_of_token, block_table, max_pages,
+                             num_pages, hq, hkv, page_size, window, scale, splits, scratch, counters, stream);
+  return atc_launch_pair<128>(mq, mk, mv, out, tile_row0, tile_rows, num_tiles, positions, slot_of_token, block_table, max_pages,
+                              num_pages, hq, hkv, page_size, window, scale, splits, scratch, counters, stream);
 }

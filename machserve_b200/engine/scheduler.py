@@ -45,7 +45,7 @@ from ..sampling.params import SamplingParams, advance_seed
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
 
 
-@dataclass
+@dataclass(eq=False)  # a request is itself: membership tests and removals compare identities, not fields
 class Sequence_:
     id: int
     prompt: List[int]
@@ -192,9 +192,10 @@ class Scheduler:
 
     def _schedule_once(self, preempted: List[int]) -> List[PlanEntry]:
         entries: List[PlanEntry] = []
+        in_plan = set()  # ids of the requests that have an entry
         # 1. one token for every request that is decoding, oldest first; make room by preempting the youngest
         for seq in list(self.running):
-            if seq not in self.running or seq.planned < seq.total - 1:
+            if seq.status != RUNNING or seq.planned < seq.total - 1:
                 continue
             if seq.pending > 1:
                 continue  # its next token is not even on the device yet: only the preceding step's samples are
@@ -203,21 +204,22 @@ class Scheduler:
                 continue
             while not self.cache.can_reserve(seq.id, seq.total):
                 victim = self.running[-1]
-                planned = [e for e in entries if e.seq is victim]
-                for e in planned:
-                    entries.remove(e)
+                if victim.id in in_plan:
+                    entries[:] = [e for e in entries if e.seq is not victim]
+                    in_plan.discard(victim.id)
                 self._preempt(victim, preempted)
                 if victim is seq:
                     break
-            if seq in self.running:
+            if seq.status == RUNNING:
                 self.cache.reserve(seq.id, seq.total)
                 entries.append(PlanEntry(seq, seq.total - 1, 1, True, seq.preemptions, seq.pending > 0))
+                in_plan.add(seq.id)
         # 2. portions of prompts under the budget: running requests first, then admissions
         budget = self.prefill_rows
         for seq in list(self.running):
             if budget == 0:
                 break
-            if seq.planned >= seq.known - 1 or any(e.seq is seq for e in entries):
+            if seq.planned >= seq.known - 1 or seq.id in in_plan:
                 continue
             budget -= self._plan_portion(seq, budget, entries)
         while self.waiting and budget > 0 and len(self.running) < self.capacity:

@@ -112,12 +112,13 @@ class Attention(Mixer):
         """Rows that are alone in their sequence (decoding) go to the kernel that splits a row's keys over blocks;
         portions of prompts are cut into tiles of up to 64 and up to 128 consecutive rows for the two prompt kernels."""
         single, t0, tn, b0, bn = [], [], [], [], []
-        longest = 0
+        longest = longest_portion = 0  # the most keys a decoding row sees, and a row of a portion
         for row, n, start in zip(step.row0, step.count, step.start):
             if n == 1:
                 single.append(row)
                 longest = max(longest, start + 1)
             else:
+                longest_portion = max(longest_portion, start + n)
                 for a in range(0, n, self.TILE):
                     t0.append(row + a)
                     tn.append(min(self.TILE, n - a))
@@ -125,7 +126,7 @@ class Attention(Mixer):
                     b0.append(row + a)
                     bn.append(min(self.BIG_TILE, n - a))
         lists = {"single_rows": single, "tile_row0": t0, "tile_rows": tn, "big_tile_row0": b0, "big_tile_rows": bn}
-        return WorkPlan(lists, (-(-longest // self.CONTEXT_BUCKET),))
+        return WorkPlan(lists, (-(-longest // self.CONTEXT_BUCKET), -(-longest_portion // self.CONTEXT_BUCKET)))
 
     # -- with few rows in bfloat16: the norm in front and the add behind inside the products -------------------------
     fused_rows = 16
@@ -251,10 +252,20 @@ class Attention(Mixer):
         if sizes["single_rows"]:
             self._attend_single(ctx, q, cache, out)
         if sizes["big_tile_row0"] and self.tc_prefill and cache.k_pages.shape[2] in self.tc_pages:
-            # portions of prompts on the tcgen05 tensor cores, in tiles of up to 128 rows
+            # portions of prompts on the tcgen05 tensor cores, in tiles of up to 128 rows; with few tiles the keys of
+            # each are split over several blocks (chosen from the longest portion's keys, by bucket)
+            n_tiles = sizes["big_tile_row0"]
+            max_keys = work.shape[1] * self.CONTEXT_BUCKET
+            if self.window:
+                max_keys = min(max_keys, self.window + self.BIG_TILE)
+            splits = ops.attention_prefill_tc_splits(n_tiles, self.hq, self.hkv, self.hd, max_keys)
+            scratch = None
+            if splits > 1:
+                words = ops.attention_prefill_tc_scratch_words(n_tiles, self.hq, self.hd, splits)
+                scratch = rt.workspace.get("attn.prefill_splits", (words,), torch.float32, zero=True)
             ops.attention_prefill_tc(
-                q, cache.k_pages, cache.v_pages, out, lists["big_tile_row0"], lists["big_tile_rows"], sizes["big_tile_row0"],
-                ctx.positions, ctx.slot_of_token, table, self.hq, self.hkv, self.hd, self.window, self.scale,
+                q, cache.k_pages, cache.v_pages, out, lists["big_tile_row0"], lists["big_tile_rows"], n_tiles,
+                ctx.positions, ctx.slot_of_token, table, self.hq, self.hkv, self.hd, self.window, self.scale, splits, scratch,
             )
         elif sizes["tile_row0"]:
             ops.attention_prefill(

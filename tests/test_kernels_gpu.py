@@ -435,9 +435,12 @@ TC_ATT_CASES = [
 ]
 
 
+@pytest.mark.parametrize("splits", [1, 2, 3, 4])
 @pytest.mark.parametrize("lens,hq,hkv,hd,page,window", TC_ATT_CASES)
-def test_attention_prefill_tc(lens, hq, hkv, hd, page, window):
-    """The tcgen05 kernel for portions of prompts: tiles of up to 128 rows, pages of several sizes, windows."""
+def test_attention_prefill_tc(lens, hq, hkv, hd, page, window, splits):
+    """The tcgen05 kernel for portions of prompts: tiles of up to 128 rows, pages of several sizes, windows; the key
+    tiles of every (tile, head) in one run or split over two to four blocks that merge through scratch memory.  Run
+    twice on the same scratch memory: a launch leaves its counters as it found them."""
     import torch
     from machserve_b200 import ops
     assert ops.attention_prefill_tc_supports(hd, page)
@@ -453,12 +456,34 @@ def test_attention_prefill_tc(lens, hq, hkv, hd, page, window):
                 rows += [(s, p) for p in range(t0, min(t0 + 128, b))]
     far = (len(rows) - 1, hq - 1, max(0, rows[-1][1] - window + 1) if window else 0)
     q, want, pos, slot = case.queries(rows, scale_one=far)
-    out = torch.full((len(rows), hq * hd), 7.0, dtype=torch.bfloat16, device=dev())
-    ops.attention_prefill_tc(T(q, torch.bfloat16), case.k_pages, case.v_pages, out, T(np.array(tile0, dtype=np.int32)),
-                             T(np.array(tilen, dtype=np.int32)), len(tile0), pos, slot, case.table, hq, hkv, hd, window, hd ** -0.5)
-    assert ops.gemm_tc_status() == 0
-    err = np.abs(N(out) - want).max(axis=1)
-    assert err.max() <= 2.0 ** -7 * max(1.0, np.abs(want).max()), f"worst row {int(err.argmax())} of {len(rows)}: {rows[int(err.argmax())]}"
+    words = ops.attention_prefill_tc_scratch_words(len(tile0), hq, hd, splits)
+    assert (words == 0) == (splits == 1)
+    scratch = torch.zeros(words, dtype=torch.float32, device=dev()) if words else None
+    for again in range(2):
+        out = torch.full((len(rows), hq * hd), 7.0, dtype=torch.bfloat16, device=dev())
+        ops.attention_prefill_tc(T(q, torch.bfloat16), case.k_pages, case.v_pages, out, T(np.array(tile0, dtype=np.int32)),
+                                 T(np.array(tilen, dtype=np.int32)), len(tile0), pos, slot, case.table, hq, hkv, hd, window,
+                                 hd ** -0.5, splits, scratch)
+        assert ops.gemm_tc_status() == 0
+        err = np.abs(N(out) - want).max(axis=1)
+        assert err.max() <= 2.0 ** -7 * max(1.0, np.abs(want).max()), f"worst row {int(err.argmax())} of {len(rows)}: {rows[int(err.argmax())]}"
+    if scratch is not None:
+        assert int(scratch[-len(tile0) * hq:].view(torch.int32).abs().sum()) == 0, "the counters were not left at zero"
+        with pytest.raises(ops.KernelError, match="words of scratch"):
+            ops.attention_prefill_tc(T(q, torch.bfloat16), case.k_pages, case.v_pages, out, T(np.array(tile0, dtype=np.int32)),
+                                     T(np.array(tilen, dtype=np.int32)), len(tile0), pos, slot, case.table, hq, hkv, hd, window,
+                                     hd ** -0.5, splits, scratch[:-1])
+
+
+def test_attention_prefill_tc_split_policy():
+    """Few tiles of rows against many keys are split; a launch that fills the GPU by itself is not."""
+    from machserve_b200 import ops
+    assert ops.attention_prefill_tc_splits(64, 14, 2, 64, 8192) == 1
+    assert ops.attention_prefill_tc_splits(4, 14, 2, 64, 2048) == 4
+    assert ops.attention_prefill_tc_splits(16, 14, 2, 64, 2048) == 1  # 224 blocks for 296 places
+    assert ops.attention_prefill_tc_splits(4, 12, 2, 128, 2048) == 4
+    assert ops.attention_prefill_tc_splits(4, 12, 2, 128, 512) == 1  # too few keys to split
+    assert ops.attention_prefill_tc_splits(1, 2, 1, 64, 1024) == 2
 
 
 @pytest.mark.parametrize("k_gain", [None, 48.0])
