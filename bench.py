@@ -187,9 +187,10 @@ def time_attention_prefill(torch, ops, a, pk) -> int:
         splits = ops.attention_prefill_tc_splits(t0.numel(), hq, hkv, hd, n)  # the engine's own choice
         words = ops.attention_prefill_tc_scratch_words(t0.numel(), hq, hd, splits)
         scratch = torch.zeros(words, dtype=torch.float32, device=dev) if words else None
+        counters = torch.zeros(t0.numel() * hq, dtype=torch.int32, device=dev) if words else None
         def run():
             ops.attention_prefill_tc(q, kp, vp, out, t0, tn, t0.numel(), pos, slot, table, hq, hkv, hd, None, hd ** -0.5,
-                                     splits, scratch)
+                                     splits, scratch, counters)
         for _ in range(max(a.warmup, 3)):
             run()
         torch.cuda.synchronize()

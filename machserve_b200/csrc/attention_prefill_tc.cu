@@ -967,11 +967,11 @@ MS_API int ms_attention_prefill_tc_supports(int hd, int page_size) {
   return (hd == 64 || hd == 128) && page_size >= 8 && (page_size & (page_size - 1)) == 0;
 }
 
-// float32 words of scratch memory that `splits` > 1 need: every item's partial results, then one counter per item
-// (which must be zero before the first launch and is left zero by every launch).
+// float32 words of scratch memory that `splits` > 1 need for the items' partial results.  Beside them the launch
+// needs num_tiles * hq counters (int32), which must be zero before the first launch and are left zero by every launch.
 MS_API long long ms_attention_prefill_tc_scratch_words(int num_tiles, int hq, int hd, int splits) {
   if (splits <= 1) return 0;
-  return (long long)num_tiles * hq * splits * ATC_SPLIT_WORDS(hd) + (long long)num_tiles * hq;
+  return (long long)num_tiles * hq * splits * ATC_SPLIT_WORDS(hd);
 }
 
 // How many runs the key tiles of every item are cut into so that a launch fills the GPU: few tiles of rows (a short
@@ -990,12 +990,13 @@ MS_API int ms_attention_prefill_tc_splits(int num_tiles, int hq, int hkv, int hd
 }
 
 // As ms_attention_prefill, with tiles of up to 128 rows.  q, out: bfloat16 [total_rows, hq*hd].  `splits` (1 to 4): the
-// key tiles of every item go to that many blocks, which meet in `scratch` (ms_attention_prefill_tc_scratch_words).
+// key tiles of every item go to that many blocks, which meet in `scratch` (ms_attention_prefill_tc_scratch_words) and
+// count themselves in `counters` (num_tiles * hq of them, all zero).
 MS_API int ms_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, void* out, int total_rows,
                                    const int* tile_row0, const int* tile_rows, int num_tiles, const int* positions,
                                    const int* slot_of_token, const int* block_table, int max_pages, int num_pages, int hq,
                                    int hkv, int hd, int page_size, int window, float scale, int splits, float* scratch,
-                                   long long scratch_words, cudaStream_t stream) {
+                                   long long scratch_words, int* counters, long long num_counters, cudaStream_t stream) {
   if (num_tiles == 0) return 0;
   MS_REQUIRE(num_tiles > 0 && total_rows > 0 && hq > 0 && hkv > 0 && hq % hkv == 0 && hq <= 65535, "attention_prefill_tc: bad sizes");
   MS_REQUIRE(ms_attention_prefill_tc_supports(hd, page_size),
@@ -1005,7 +1006,8 @@ MS_API int ms_attention_prefill_tc(const void* q, const void* k_pages, const voi
   const long long need = ms_attention_prefill_tc_scratch_words(num_tiles, hq, hd, splits);
   MS_REQUIRE(need == 0 || (scratch != nullptr && scratch_words >= need),
              "attention_prefill_tc: %d splits need %lld words of scratch memory, %lld were given", splits, need, scratch_words);
-  int* counters = need ? reinterpret_cast<int*>(scratch + (need - (long long)num_tiles * hq)) : nullptr;
+  MS_REQUIRE(need == 0 || (counters != nullptr && num_counters >= (long long)num_tiles * hq),
+             "attention_prefill_tc: %d splits need %lld counters, %lld were given", splits, (long long)num_tiles * hq, num_counters);
   CUtensorMap mq, mk, mv;
   if (int rc = atc_make_map(&mq, q, total_rows, hq * hd, hq * hd, ATC_ROWS)) return rc;
   const int box = page_size < ATC_KEYS ? page_size : ATC_KEYS;

@@ -538,6 +538,7 @@ class ModelRunner:
         """Raises if a tensor-core kernel gave up one of its bounded waits since the last check (synchronizes)."""
         gemm, attention = ops.tc_status_codes()
         if gemm or attention:
+            self.rt.workspace.rezero()  # a block that gave up may not have counted itself out
             raise RuntimeError(f"a tcgen05 kernel gave up a wait (product code {gemm}, attention code {attention}); "
                                "the results of recent steps are not valid")
 

@@ -66,7 +66,7 @@ class _Signatures:
     ms_attention_decode = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P]
     ms_attention_decode_cluster = [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, I, P]
     ms_attention_decode_cluster_rope = [P, I, P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, I, P]
-    ms_attention_prefill_tc = [P, P, P, P, I, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, LL, P]
+    ms_attention_prefill_tc = [P, P, P, P, I, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, LL, P, LL, P]
     ms_attention_prefill = [P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P]
     ms_gemm_small_m = [P, I, P, P, I, I, I, I, I, I, P]
     ms_gemm_small_m_silu_mul = [P, I, P, P, P, I, I, I, I, I, P]
@@ -590,20 +590,21 @@ def attention_prefill_tc_splits(num_tiles: int, num_heads: int, num_kv_heads: in
 
 
 def attention_prefill_tc_scratch_words(num_tiles: int, num_heads: int, head_dim: int, splits: int) -> int:
-    """float32 words of scratch memory for `splits` > 1; its tail (one counter per item) must be zero before the first
-    launch and is left zero by every launch."""
+    """float32 words of scratch memory for `splits` > 1 (beside num_tiles * num_heads int32 counters, which must be zero
+    before the first launch and are left zero by every launch)."""
     fn = lib().ms_attention_prefill_tc_scratch_words
     fn.restype = c_longlong
     return int(fn(int(num_tiles), int(num_heads), int(head_dim), int(splits)))
 
 
 def attention_prefill_tc(q, k_pages, v_pages, out, tile_row0, tile_rows, num_tiles, positions, slot_of_token, block_table,
-                         num_heads, num_kv_heads, head_dim, window, scale, splits=1, scratch=None):
+                         num_heads, num_kv_heads, head_dim, window, scale, splits=1, scratch=None, counters=None):
     """Paged causal attention for tiles of up to 128 consecutive rows of one sequence on tcgen05 tensor cores
     (TMA-fed, scores in tensor memory and taken into registers a row per thread, probabilities back into tensor
     memory, outputs accumulated there over all key tiles).  Head sizes 64 (one head per block) and 128 (two heads of a
     group per block, which share the keys and values), page sizes 8, 16, 32, ...  With `splits` > 1 the key tiles of
-    every (tile, head) go to that many blocks, which meet in `scratch` (float32, zero where the counters lie)."""
+    every (tile, head) go to that many blocks, which meet in `scratch` (float32) and count themselves in `counters`
+    (int32, num_tiles * num_heads of them, all zero before and after)."""
     _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16,
           "attention_prefill_tc: bfloat16 only")
     _need(q.is_contiguous() and out.is_contiguous() and k_pages.is_contiguous() and v_pages.is_contiguous(),
@@ -613,12 +614,14 @@ def attention_prefill_tc(q, k_pages, v_pages, out, tile_row0, tile_rows, num_til
     _need(tile_row0.dtype == torch.int32 and tile_rows.dtype == torch.int32 and min(tile_row0.numel(), tile_rows.numel()) >= num_tiles,
           "attention_prefill_tc: bad tile lists")
     _need(scratch is None or (scratch.dtype == torch.float32 and scratch.is_contiguous()), "attention_prefill_tc: scratch must be float32")
+    _need(counters is None or (counters.dtype == torch.int32 and counters.is_contiguous()), "attention_prefill_tc: counters must be int32")
     _check(
         lib().ms_attention_prefill_tc(
             _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), q.shape[0], _ptr(tile_row0), _ptr(tile_rows), int(num_tiles),
             _ptr(positions), _ptr(slot_of_token), _ptr(block_table), block_table.shape[1], k_pages.shape[0], num_heads,
             num_kv_heads, head_dim, k_pages.shape[2], int(window or 0), float(scale), int(splits), _ptr(scratch),
-            scratch.numel() if scratch is not None else 0, _stream(),
+            scratch.numel() if scratch is not None else 0, _ptr(counters), counters.numel() if counters is not None else 0,
+            _stream(),
         ),
         "attention_prefill_tc",
     )

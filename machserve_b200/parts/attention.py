@@ -259,13 +259,15 @@ class Attention(Mixer):
             if self.window:
                 max_keys = min(max_keys, self.window + self.BIG_TILE)
             splits = ops.attention_prefill_tc_splits(n_tiles, self.hq, self.hkv, self.hd, max_keys)
-            scratch = None
+            scratch = counters = None
             if splits > 1:
                 words = ops.attention_prefill_tc_scratch_words(n_tiles, self.hq, self.hd, splits)
-                scratch = rt.workspace.get("attn.prefill_splits", (words,), torch.float32, zero=True)
+                scratch = rt.workspace.get("attn.prefill_splits", (words,), torch.float32)
+                # (a buffer of its own: zero when made, left zero by every launch, wherever the partial results lie)
+                counters = rt.workspace.get("attn.prefill_counters", (n_tiles * self.hq,), torch.int32, zero=True)
             ops.attention_prefill_tc(
                 q, cache.k_pages, cache.v_pages, out, lists["big_tile_row0"], lists["big_tile_rows"], n_tiles,
-                ctx.positions, ctx.slot_of_token, table, self.hq, self.hkv, self.hd, self.window, self.scale, splits, scratch,
+                ctx.positions, ctx.slot_of_token, table, self.hq, self.hkv, self.hd, self.window, self.scale, splits, scratch, counters,
             )
         elif sizes["tile_row0"]:
             ops.attention_prefill(

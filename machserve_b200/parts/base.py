@@ -87,6 +87,7 @@ class Workspace:
         self.device = device
         self._bufs: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
         self._retired: List[torch.Tensor] = []
+        self._zeroed: set = set()  # buffers whose users rely on finding zeros (and leave zeros behind)
 
     def get(self, name: str, shape, dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
         """A view of the buffer `name`; with `zero`, the buffer is zero-filled when it is made."""
@@ -100,7 +101,14 @@ class Workspace:
                 self._retired.append(buf)  # captured graphs may still point into it
             buf = (torch.zeros if zero else torch.empty)(max(n, 1), dtype=dtype, device=self.device)
             self._bufs[key] = buf
+            if zero:
+                self._zeroed.add(key)
         return buf[:n].view(*shape)
+
+    def rezero(self) -> None:
+        """Zeros again what was handed out as zeros: after a kernel gave up half-way and may have left counters behind."""
+        for key in self._zeroed:
+            self._bufs[key].zero_()
 
     def nbytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in [*self._bufs.values(), *self._retired])

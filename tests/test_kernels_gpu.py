@@ -458,21 +458,27 @@ def test_attention_prefill_tc(lens, hq, hkv, hd, page, window, splits):
     q, want, pos, slot = case.queries(rows, scale_one=far)
     words = ops.attention_prefill_tc_scratch_words(len(tile0), hq, hd, splits)
     assert (words == 0) == (splits == 1)
-    scratch = torch.zeros(words, dtype=torch.float32, device=dev()) if words else None
+    # the scratch memory starts as garbage: only the counters have to be zero
+    scratch = torch.full((words,), float("nan"), dtype=torch.float32, device=dev()) if words else None
+    counters = torch.zeros(len(tile0) * hq, dtype=torch.int32, device=dev()) if words else None
     for again in range(2):
         out = torch.full((len(rows), hq * hd), 7.0, dtype=torch.bfloat16, device=dev())
         ops.attention_prefill_tc(T(q, torch.bfloat16), case.k_pages, case.v_pages, out, T(np.array(tile0, dtype=np.int32)),
                                  T(np.array(tilen, dtype=np.int32)), len(tile0), pos, slot, case.table, hq, hkv, hd, window,
-                                 hd ** -0.5, splits, scratch)
+                                 hd ** -0.5, splits, scratch, counters)
         assert ops.gemm_tc_status() == 0
         err = np.abs(N(out) - want).max(axis=1)
         assert err.max() <= 2.0 ** -7 * max(1.0, np.abs(want).max()), f"worst row {int(err.argmax())} of {len(rows)}: {rows[int(err.argmax())]}"
     if scratch is not None:
-        assert int(scratch[-len(tile0) * hq:].view(torch.int32).abs().sum()) == 0, "the counters were not left at zero"
+        assert int(counters.abs().sum()) == 0, "the counters were not left at zero"
         with pytest.raises(ops.KernelError, match="words of scratch"):
             ops.attention_prefill_tc(T(q, torch.bfloat16), case.k_pages, case.v_pages, out, T(np.array(tile0, dtype=np.int32)),
                                      T(np.array(tilen, dtype=np.int32)), len(tile0), pos, slot, case.table, hq, hkv, hd, window,
-                                     hd ** -0.5, splits, scratch[:-1])
+                                     hd ** -0.5, splits, scratch[:-1], counters)
+        with pytest.raises(ops.KernelError, match="counters"):
+            ops.attention_prefill_tc(T(q, torch.bfloat16), case.k_pages, case.v_pages, out, T(np.array(tile0, dtype=np.int32)),
+                                     T(np.array(tilen, dtype=np.int32)), len(tile0), pos, slot, case.table, hq, hkv, hd, window,
+                                     hd ** -0.5, splits, scratch, counters[:-1])
 
 
 def test_attention_prefill_tc_split_policy():
