@@ -8,6 +8,9 @@
 // an online softmax, and the four partial results are merged in warp order.  So the
 // arithmetic for a token depends on its position alone: not on how the sequence was
 // cut into steps, not on what else is in the batch, not on which pages hold the keys.
+// A warp brings its tile of keys into shared memory row by row (every load a whole row,
+// consecutive lanes consecutive elements) and each lane then takes the dot product of
+// the query with its own key from there; the values are read row by row as they are.
 //
 // Counterparts in gqf2008/machserve (crates/mach-model/src/kernels.rs):
 // attn_decode_batched :1083-1141 (two-pass, one block per row and head),
@@ -28,6 +31,7 @@ attention_generic_kernel(const TA* __restrict__ q, const TC* __restrict__ k_page
   __shared__ float q_s[ATT_MAX_HD];
   __shared__ float acc_s[ATT_WARPS][ATT_MAX_HD];
   __shared__ float m_s[ATT_WARPS], l_s[ATT_WARPS];
+  extern __shared__ float key_tiles[];  // [warp][key of the tile][hd + 1]: the odd stride keeps the lanes' rows in different banks
 
   const int t = blockIdx.x / hq, h = blockIdx.x - t * hq;
   const int seq = seq_of_token[t];
@@ -50,20 +54,36 @@ attention_generic_kernel(const TA* __restrict__ q, const TC* __restrict__ k_page
   const size_t head_off = (size_t)kvh * page_size * hd;
   const size_t page_elems = (size_t)hkv * page_size * hd;
 
+  float* my_keys = key_tiles + (size_t)warp * 32 * (hd + 1);
   for (int tile = first_key / 32 + warp; tile * 32 <= pos; tile += ATT_WARPS) {
     const int key = tile * 32 + lane;
     const bool valid = key >= first_key && key <= pos;
     long long base = -1;  // element offset of this lane's key row inside the pages
-    float s = -INFINITY;
     if (valid) {
       const int page = table[key / page_size];
-      if (page >= 0 && page < num_pages) {
-        base = (long long)((size_t)page * page_elems + head_off + (size_t)(key % page_size) * hd);
-        const TC* kr = k_pages + base;
-        float dot = 0.f;
-        for (int d = 0; d < hd; ++d) dot = fmaf(q_s[d], ms_to_float(kr[d]), dot);
-        s = dot * scale;
+      if (page >= 0 && page < num_pages) base = (long long)((size_t)page * page_elems + head_off + (size_t)(key % page_size) * hd);
+    }
+    __syncwarp();  // the tile before has been read
+    // eight rows at a time, so that eight loads are in flight per lane
+    for (int j0 = 0; j0 < 32; j0 += 8) {
+      long long b[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) b[u] = __shfl_sync(0xffffffffu, base, j0 + u);
+      for (int d = lane; d < hd; d += 32) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = b[u] >= 0 ? ms_to_float(k_pages[b[u] + d]) : 0.f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) my_keys[(j0 + u) * (hd + 1) + d] = v[u];
       }
+    }
+    __syncwarp();
+    float s = -INFINITY;
+    if (base >= 0) {
+      const float* kr = my_keys + lane * (hd + 1);
+      float dot = 0.f;
+      for (int d = 0; d < hd; ++d) dot = fmaf(q_s[d], kr[d], dot);
+      s = dot * scale;
     }
     const float tile_max = ms_warp_max(s);
     const float m_new = fmaxf(m, tile_max);
@@ -73,15 +93,26 @@ attention_generic_kernel(const TA* __restrict__ q, const TC* __restrict__ k_page
     l = l * corr + ms_warp_sum(p);
 #pragma unroll
     for (int i = 0; i < NACC; ++i) acc[i] *= corr;
-    for (int j = 0; j < 32; ++j) {
-      const long long bj = __shfl_sync(0xffffffffu, base, j);
-      if (bj < 0) continue;  // same for the whole warp
-      const float pj = __shfl_sync(0xffffffffu, p, j);
-      const TC* vr = v_pages + bj;
+    // the values of eight keys at a time (eight loads in flight), added key by key in ascending order
+    for (int j0 = 0; j0 < 32; j0 += 8) {
+      long long b[8];
+      float pj[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        b[u] = __shfl_sync(0xffffffffu, base, j0 + u);
+        pj[u] = __shfl_sync(0xffffffffu, p, j0 + u);
+      }
 #pragma unroll
       for (int i = 0; i < NACC; ++i) {
         const int d = lane + 32 * i;
-        if (d < hd) acc[i] = fmaf(pj, ms_to_float(vr[d]), acc[i]);
+        if (d < hd) {
+          float v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) v[u] = b[u] >= 0 ? ms_to_float(v_pages[b[u] + d]) : 0.f;
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (b[u] >= 0) acc[i] = fmaf(pj[u], v[u], acc[i]);
+        }
       }
     }
     m = m_new;
@@ -124,10 +155,20 @@ MS_API int ms_attention_generic(const void* q, const void* k_pages, const void* 
   MS_REQUIRE(hd > 0 && hd <= ATT_MAX_HD, "attention: head_dim %d is outside (0, %d]", hd, ATT_MAX_HD);
   MS_REQUIRE(page_size > 0 && max_pages > 0 && num_pages > 0, "attention: bad cache sizes");
   const unsigned blocks = (unsigned)tokens * (unsigned)hq;
+  const size_t smem = (size_t)ATT_WARPS * 32 * (hd + 1) * sizeof(float);
 #define MS_ATT_CASE(TA, TC)                                                                                     \
-  attention_generic_kernel<TA, TC><<<blocks, ATT_WARPS * 32, 0, stream>>>(                                     \
-      (const TA*)q, (const TC*)k_pages, (const TC*)v_pages, (TA*)out, positions, seq_of_token, block_table,    \
-      max_pages, num_pages, hq, hkv, hd, page_size, window, scale)
+  do {                                                                                                          \
+    static bool configured = false;                                                                             \
+    if (!configured) {                                                                                          \
+      cudaError_t e = cudaFuncSetAttribute(attention_generic_kernel<TA, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                           (int)((size_t)ATT_WARPS * 32 * (ATT_MAX_HD + 1) * sizeof(float)));   \
+      MS_REQUIRE(e == cudaSuccess, "attention: cannot get shared memory for the key tiles: %s", cudaGetErrorString(e)); \
+      configured = true;                                                                                        \
+    }                                                                                                           \
+    attention_generic_kernel<TA, TC><<<blocks, ATT_WARPS * 32, smem, stream>>>(                                \
+        (const TA*)q, (const TC*)k_pages, (const TC*)v_pages, (TA*)out, positions, seq_of_token, block_table,  \
+        max_pages, num_pages, hq, hkv, hd, page_size, window, scale);                                          \
+  } while (0)
   if (act_dtype == MS_F32 && cache_dtype == MS_F32)
     MS_ATT_CASE(float, float);
   else if (act_dtype == MS_BF16 && cache_dtype == MS_BF16)

@@ -63,12 +63,62 @@ gemm_f32_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ 
   }
 }
 
+// The same sums for up to 16 rows (decoding), laid out for streaming the weights: a block of 128 threads takes 8
+// weight rows, thread (n, m) owns out[m][n] and adds its products for k = 0..K-1 in ascending order, exactly as
+// the kernel above does, so a row's result is the same bit for bit whichever of the two computed it.  With 8
+// weight rows per block a matrix of 896 rows is spread over 112 blocks (the kernel above would use 14).
+#define G32S_ROWS 16
+#define G32S_COLS 8
+#define G32S_KT 128
+
+__global__ void __launch_bounds__(G32S_ROWS * G32S_COLS)
+gemm_f32_small_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ w, const float* __restrict__ bias,
+                      float* __restrict__ out, int ldo, int M, int N, int K) {
+  __shared__ __align__(16) float ws[G32S_COLS][G32S_KT + 4];
+  __shared__ __align__(16) float xs[G32S_ROWS][G32S_KT + 4];
+  const int tid = threadIdx.x, nl = tid >> 4, m = tid & 15;
+  const int n0 = blockIdx.x * G32S_COLS;
+  float acc = 0.f;
+  for (int k0 = 0; k0 < K; k0 += G32S_KT) {
+#pragma unroll
+    for (int i = 0; i < G32S_COLS; ++i) {  // 8 x 128 weights: a row of 128 consecutive k per 128 threads
+      const int gk = k0 + tid;
+      ws[i][tid] = (n0 + i < N && gk < K) ? w[(size_t)(n0 + i) * K + gk] : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < G32S_ROWS; ++i) {
+      const int gk = k0 + tid;
+      xs[i][tid] = (i < M && gk < K) ? x[(size_t)i * ldx + gk] : 0.f;
+    }
+    __syncthreads();
+    const int kn = K - k0 < G32S_KT ? K - k0 : G32S_KT;
+    int c = 0;
+    for (; c + 4 <= kn; c += 4) {
+      const float4 a = *reinterpret_cast<const float4*>(&xs[m][c]);
+      const float4 b = *reinterpret_cast<const float4*>(&ws[nl][c]);
+      acc = fmaf(a.x, b.x, acc);
+      acc = fmaf(a.y, b.y, acc);
+      acc = fmaf(a.z, b.z, acc);
+      acc = fmaf(a.w, b.w, acc);
+    }
+    for (; c < kn; ++c) acc = fmaf(xs[m][c], ws[nl][c], acc);
+    __syncthreads();
+  }
+  const int n = n0 + nl;
+  if (m < M && n < N) out[(size_t)m * ldo + n] = acc + (bias ? bias[n] : 0.f);
+}
+
 // x: [M, K] with row stride ldx; w: [N, K] dense; out: [M, N] with row stride ldo.
 MS_API int ms_gemm_f32(const float* x, int ldx, const float* w, const float* bias, float* out, int ldo, int M, int N,
                        int K, cudaStream_t stream) {
   if (M == 0) return 0;
   MS_REQUIRE(M > 0 && N > 0 && K > 0 && ldx >= K && ldo >= N, "gemm_f32: bad sizes M=%d N=%d K=%d ldx=%d ldo=%d", M, N, K,
              ldx, ldo);
+  if (M <= G32S_ROWS) {
+    gemm_f32_small_kernel<<<(N + G32S_COLS - 1) / G32S_COLS, G32S_ROWS * G32S_COLS, 0, stream>>>(x, ldx, w, bias, out, ldo, M, N, K);
+    MS_LAUNCH_CHECK("gemm_f32");
+    return 0;
+  }
   dim3 grid((N + G32_BN - 1) / G32_BN, (M + G32_BM - 1) / G32_BM);
   MS_REQUIRE(grid.y <= 65535, "gemm_f32: %d rows are more than one launch takes", M);
   gemm_f32_kernel<<<grid, 256, 0, stream>>>(x, ldx, w, bias, out, ldo, M, N, K);
