@@ -501,12 +501,13 @@ class ModelRunner:
         return logits
 
     MAX_SHAPE_GRAPHS = 24
+    CAPTURE_AFTER = 3  # a capture costs as much as some tens of such steps run plainly: only shapes that keep coming
 
     def _step_general(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        """A step of any shape.  A shape that comes a second time (the same numbers of rows, sequences, wanted rows,
-        single rows and tiles: a server's steady portions, a benchmark's prompt) is captured in a CUDA graph and
-        replayed from then on: the index arrays lie at the same places of the staging buffer, only their
-        contents change."""
+        """A step of any shape.  A shape that keeps coming (the same numbers of rows, sequences and wanted rows and the
+        same work lists: a server's steady portions, a benchmark's prompt) is captured in a CUDA graph at its fourth
+        occurrence and replayed from then on: the index arrays lie at the same places of the staging buffer, only
+        their contents change."""
         ctx = self._stage(entries)
         if not self.use_graphs:
             return self.model.forward(ctx, self.bindings)
@@ -520,11 +521,11 @@ class ModelRunner:
             return logits
         seen = self._shape_seen.get(key, 0)
         self._shape_seen[key] = seen + 1
-        if seen == 0 or len(self._shape_graphs) >= self.MAX_SHAPE_GRAPHS:
+        if seen < self.CAPTURE_AFTER or len(self._shape_graphs) >= self.MAX_SHAPE_GRAPHS:
             if len(self._shape_seen) > 4096:
                 self._shape_seen.clear()
             return self.model.forward(ctx, self.bindings)
-        # second time: the scratch memory has its size and every kernel has been loaded by the first
+        # the scratch memory has its size and every kernel has been loaded by the runs before
         before = ops.launches()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):

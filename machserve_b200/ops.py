@@ -103,7 +103,14 @@ def _check(code: int, name: str) -> None:
         raise KernelError(f"{name}: {lib().ms_last_error().decode()}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> c_void_p:
+    """The current stream's handle (the capturing stream while a graph is captured).  Asked for with every launch, so
+    through torch's raw getter where it exists: `torch.cuda.current_stream()` builds a Python object each time."""
+    if _raw_stream is not None:
+        return c_void_p(_raw_stream(torch.cuda.current_device()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
