@@ -1,4 +1,4 @@
-"""The command line: `mach generate | replay | random | bench`.
+"""The command line: `mach generate | replay | random | bench | timeline`.
 
 The reference is configured by environment variables of its server
 (crates/mach-server/src/main.rs:7-37 of gqf2008/machserve); the options here carry
@@ -159,6 +159,10 @@ def main(argv=None) -> int:
     b.add_argument("--warmup", type=int, default=5)
     b.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (named in the output)")
     b.set_defaults(fn=cmd_bench)
+
+    t = sub.add_parser("timeline", help="device-side timeline of one decoding step (python -m machserve_b200.timeline)")
+    t.add_argument("rest", nargs=argparse.REMAINDER)
+    t.set_defaults(fn=lambda a: __import__("machserve_b200.timeline", fromlist=["main"]).main(a.rest))
 
     a = ap.parse_args(argv)
     return a.fn(a)

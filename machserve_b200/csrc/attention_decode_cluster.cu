@@ -95,7 +95,13 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [16][STRIDE]
   __nv_bfloat16* kv_s = q_s + 16 * STRIDE;                           // [stages][K, V][DCL_TILE][STRIDE]
-  __shared__ float fin_m[16], fin_l[16];
+  // What the blocks of a cluster hand each other at the end: block k puts its part of (head, coordinate) pair e into
+  // the shared memory of the block that merges e, at [k][e - that block's first pair], and its heads' maxima and
+  // sums into every block's.  Nothing else lives here, so the others may write while this block still attends.
+  __shared__ float gath_o[16 * HD + 8];
+  __shared__ float gath_m[8][16], gath_l[8][16];
+
+  MS_TIMELINE_BEGIN(200);
   ms_pdl_trigger();
   // everything up to the wait reads only what no kernel of this step writes: the step's index arrays,
   // the block tables, and keys and values of positions before the current one
@@ -122,6 +128,7 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
                      first_key, pos, pos, tid);
 
   ms_pdl_wait();
+  MS_TIMELINE_WAITED();
 
   const int ptile = pos / DCL_TILE;
   bool row_done = false;  // the current position's key and value are in place (fused form)
@@ -221,6 +228,8 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
     }
     ms_cp_async_commit();
   }
+
+  MS_TIMELINE_MARK(0);
   MsRowState<HD> st;
   st.init();
   unsigned qa[HD / 16][4];
@@ -254,6 +263,7 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
     }
   }
   __syncthreads();  // the stages are used for the merge next
+  MS_TIMELINE_MARK(1);
 
   // merge the four warps of the block in warp order
 #pragma unroll
@@ -264,7 +274,6 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
   float* red_o = reinterpret_cast<float*>(kv_s);       // [DCL_WARPS][16][HD]
   float* red_m = red_o + DCL_WARPS * 16 * HD;          // [DCL_WARPS][16]
   float* red_l = red_m + DCL_WARPS * 16;               // [DCL_WARPS][16]
-  float* fin_o = red_l + DCL_WARPS * 16;               // [16][HD]: this block's result, relative to fin_m
   const int g0 = lane >> 2, c0 = 2 * (lane & 3);
 #pragma unroll
   for (int j = 0; j < HD / 8; ++j) {
@@ -279,7 +288,10 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
     red_l[warp * 16 + g0 + 8] = st.l[1];
   }
   __syncthreads();
-  for (int e = tid; e < groups * HD; e += DCL_THREADS) {
+  cg::cluster_group cluster = cg::this_cluster();
+  const int total = groups * HD;
+  const int per_share = (total + num_splits - 1) / num_splits;  // pairs a block of the cluster merges
+  for (int e = tid; e < total; e += DCL_THREADS) {
     const int r = e / HD, d = e - r * HD;
     float m = -INFINITY;
 #pragma unroll
@@ -295,33 +307,37 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
     if (num_splits == 1) {
       if (live) out[((size_t)t * hq + kvh * groups + r) * HD + d] = __float2bfloat16_rn(l > 0.f ? __fdividef(o, l) : 0.f);
     } else {
-      fin_o[r * HD + d] = o;
+      // to the block that merges this pair (stores through distributed shared memory: one way, no round trip)
+      const int owner = e / per_share;
+      cluster.map_shared_rank(gath_o, owner)[split * per_share + (e - owner * per_share)] = o;
       if (d == 0) {
-        fin_m[r] = m;
-        fin_l[r] = l;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          if (k < num_splits) {
+            cluster.map_shared_rank(&gath_m[0][0], k)[split * 16 + r] = m;
+            cluster.map_shared_rank(&gath_l[0][0], k)[split * 16 + r] = l;
+          }
       }
     }
   }
   if (num_splits == 1) return;
 
-  // merge the blocks of the cluster in rank order through distributed shared memory.  Every block merges its
-  // share of the (head, coordinate) pairs, and a thread first requests all it needs from the other blocks
-  // (independent loads, one round trip) and then adds in rank order, so the result does not depend on timing.
-  cg::cluster_group cluster = cg::this_cluster();
+  // One cluster barrier makes the stores visible; then every block merges its share of the pairs in rank order from
+  // its own shared memory, so the result does not depend on timing, and no block has to outlive another.
+  MS_TIMELINE_MARK(2);
   cluster.sync();
+  MS_TIMELINE_MARK(3);
   {
-    const int total = groups * HD;
-    const int per = (total + num_splits - 1) / num_splits;
-    const int e_end = min(total, (split + 1) * per);
-    for (int e = split * per + tid; e < e_end; e += DCL_THREADS) {
+    const int e_end = min(total, (split + 1) * per_share);
+    for (int e = split * per_share + tid; e < e_end; e += DCL_THREADS) {
       const int r = e / HD, d = e - r * HD;
       float mk[8], lk[8], ok[8];
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
         const bool in = k < num_splits;
-        mk[k] = in ? cluster.map_shared_rank(fin_m, in ? k : 0)[r] : -INFINITY;
-        lk[k] = in ? cluster.map_shared_rank(fin_l, in ? k : 0)[r] : 0.f;
-        ok[k] = in ? cluster.map_shared_rank(fin_o, in ? k : 0)[r * HD + d] : 0.f;
+        mk[k] = in ? gath_m[k][r] : -INFINITY;
+        lk[k] = in ? gath_l[k][r] : 0.f;
+        ok[k] = in ? gath_o[k * per_share + (e - split * per_share)] : 0.f;
       }
       float m = -INFINITY;
 #pragma unroll
@@ -336,7 +352,7 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
       if (live) out[((size_t)t * hq + kvh * groups + r) * HD + d] = __float2bfloat16_rn(l > 0.f ? __fdividef(o, l) : 0.f);
     }
   }
-  cluster.sync();  // a block's shared memory must live until the others have read it
+  MS_TIMELINE_MARK(4);
 }
 
 static size_t dcl_smem_bytes(int hd, int stages, int DCL_WARPS) {
@@ -407,6 +423,7 @@ static int launch_decode_cluster(const void* q, DclRaw raw, const void* k_pages,
 #undef MS_DCL_LAUNCH
 }
 
+MS_TIMELINE_SETTER(ms_timeline_set_attention_decode_cluster)
 
 // The most tiles a block can hold at once for a head size (about 100 KB of shared memory).
 MS_API int ms_attention_decode_cluster_max_stages(int hd) {

@@ -36,6 +36,12 @@ NVCC_FLAGS = [
 # No fast-math flag on purpose: expf, rsqrtf and division keep their accurate forms.
 
 
+# Other builds of the same sources: a name, the flags it adds, and a build folder of its own beside the plain one.
+# "timeline": the kernels of a decoding step stamp the device clock at their start, when their wait for the preceding
+# kernel returns and at their end (launch.cuh); read by machserve_b200/timeline.py.
+FLAVORS = {"timeline": ["-DMS_TIMELINE"]}
+
+
 class BuildError(RuntimeError):
     pass
 
@@ -44,12 +50,20 @@ def sources():
     return sorted(CSRC.glob("*.cu"))
 
 
-def _fingerprint() -> str:
+def _flags(flavor) -> list:
+    if flavor is None:
+        return list(NVCC_FLAGS)
+    if flavor not in FLAVORS:
+        raise BuildError(f"unknown build flavor '{flavor}' (known: {', '.join(sorted(FLAVORS))})")
+    return NVCC_FLAGS + FLAVORS[flavor]
+
+
+def _fingerprint(flavor=None) -> str:
     h = hashlib.sha256()
     for p in sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))):
         h.update(p.name.encode())
         h.update(p.read_bytes())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(_flags(flavor)).encode())
     return h.hexdigest()[:16]
 
 
@@ -76,17 +90,21 @@ def _writable_dir(path: Path) -> bool:
         return False
 
 
-def build_dir() -> Path:
+def _folder(flavor) -> str:
+    return "_build" if flavor is None else f"_build_{flavor}"
+
+
+def build_dir(flavor=None) -> Path:
     override = os.environ.get("MACHSERVE_B200_BUILD_DIR")
     if override:
-        p = Path(override)
+        p = Path(override) if flavor is None else Path(override) / flavor
         if not _writable_dir(p):
             raise BuildError(f"MACHSERVE_B200_BUILD_DIR={override} cannot be written")
         return p
-    in_tree = CSRC / "_build"
+    in_tree = CSRC / _folder(flavor)
     if _writable_dir(in_tree):
         return in_tree
-    p = Path(tempfile.gettempdir()) / f"machserve_b200_build_{os.getuid()}"
+    p = Path(tempfile.gettempdir()) / f"machserve_b200{_folder(flavor)}_{os.getuid()}"
     if not _writable_dir(p):
         raise BuildError(f"neither {in_tree} nor {p} can be written; set MACHSERVE_B200_BUILD_DIR")
     return p
@@ -96,28 +114,28 @@ def _say(msg: str) -> None:
     print(f"[machserve_b200] {msg}", file=sys.stderr, flush=True)
 
 
-def library_path(verbose: bool = True) -> Path:
-    """The path of the current library, building it first if it is missing or stale."""
-    in_tree = CSRC / "_build"
-    fp = _fingerprint()
+def library_path(verbose: bool = True, flavor=None) -> Path:
+    """The path of the current library (of the plain build, or of a flavor), building it first if it is missing or stale."""
+    in_tree = CSRC / _folder(flavor)
+    fp = _fingerprint(flavor)
     # a current library that came with the tree is used even when the tree is read-only
     if (in_tree / LIB_NAME).is_file() and (in_tree / "stamp").is_file() and (in_tree / "stamp").read_text() == fp:
         return in_tree / LIB_NAME
-    out = build_dir()
+    out = build_dir(flavor)
     lib, stamp = out / LIB_NAME, out / "stamp"
     with open(out / "lock", "w") as lock:
         fcntl.flock(lock, fcntl.LOCK_EX)
         try:
             if lib.is_file() and stamp.is_file() and stamp.read_text() == fp:
                 return lib
-            _compile(out, lib, verbose)
+            _compile(out, lib, verbose, _flags(flavor))
             stamp.write_text(fp)
             return lib
         finally:
             fcntl.flock(lock, fcntl.LOCK_UN)
 
 
-def _compile(out: Path, lib: Path, verbose: bool) -> None:
+def _compile(out: Path, lib: Path, verbose: bool, flags) -> None:
     nvcc = find_nvcc()
     srcs = sources()
     if not srcs:
@@ -129,7 +147,7 @@ def _compile(out: Path, lib: Path, verbose: bool) -> None:
     for src in srcs:
         obj = out / (src.stem + ".o")
         log = open(out / (src.stem + ".log"), "w")
-        cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+        cmd = [nvcc, *flags, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
         procs.append((src, obj, log, subprocess.Popen(cmd, stdout=log, stderr=subprocess.STDOUT)))
     last = time.time()
     while True:

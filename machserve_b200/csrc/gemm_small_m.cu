@@ -32,6 +32,7 @@
 
 namespace cg = cooperative_groups;
 
+#define GSM_MAX_CLUSTER 4  // most blocks that share the k range of the same weight rows
 #define GSM_HELD 3         // most chunks of weights a warp requests into registers before the wait
 #define GSM_PF 4           // chunks of weights a warp keeps in flight in registers (past the staged ones)
 
@@ -117,11 +118,14 @@ gemm_small_m_kernel(const void* __restrict__ x_any, int ldx, const __nv_bfloat16
                     void* __restrict__ out, int ldo, int M, int K, GsmShape sh, GsmExtra ex) {
   constexpr int THREADS = W * 32, WR = W / RB, COLS = MT * 8;
   constexpr int TPR = THREADS / COLS;  // threads that share a row of the activations: 4 .. 32, within one warp
+  MS_TIMELINE_BEGIN(100 + EPI * 10 + SCALE);
   extern __shared__ __align__(16) uint4 gsm_dyn[];
   // dynamic: [warp][staged][rows 0..7 | rows 8..15][lane] weights; then (XS) activations [COLS][xs_stride]
   // bfloat16
   __shared__ float red[W][16][COLS + 1];
   __shared__ float part[RB][16][COLS + 1];
+  // block 0 of a cluster: the other blocks' sums (with up to 16 batch rows; with more it fetches them)
+  __shared__ float gathered[MT <= 2 ? GSM_MAX_CLUSTER - 1 : 1][RB][16][COLS + 1];
   __shared__ float inv_rms[COLS];
   const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(x_any);
   const int cluster_size = sh.cluster_size, staged = sh.staged;
@@ -172,6 +176,7 @@ gemm_small_m_kernel(const void* __restrict__ x_any, int ldx, const __nv_bfloat16
   }
   ms_pdl_trigger();
   ms_pdl_wait();
+  MS_TIMELINE_WAITED();
 
   // the residual epilogue's own elements of the old residual, requested now so that they are there when the sum is
   constexpr int OUT_ELEMS = RB * 16 * COLS;
@@ -222,6 +227,7 @@ gemm_small_m_kernel(const void* __restrict__ x_any, int ldx, const __nv_bfloat16
   }
   asm volatile("cp.async.wait_group 0;\n" ::: "memory");  // staged weights: a thread reads only what it copied itself
   if (XS || SCALE) __syncthreads();
+  MS_TIMELINE_MARK(0);
 
   if (XS) {
     // the B fragments of the warp's u-th chunk come from shared memory
@@ -270,6 +276,7 @@ gemm_small_m_kernel(const void* __restrict__ x_any, int ldx, const __nv_bfloat16
         gsm_chunk<MT>(acc, wa[u], wb[u], x, ldx, M, K, (ch0 + (u1 + u) * stride) * 32, g, c);
     }
   }
+  MS_TIMELINE_MARK(2);
 
   // add the warps that share rows, in warp order
 #pragma unroll
@@ -288,8 +295,33 @@ gemm_small_m_kernel(const void* __restrict__ x_any, int ldx, const __nv_bfloat16
     for (int w = 0; w < WR; ++w) s += red[b * WR + w][r][m];
     part[b][r][m] = s;
   }
-  // add the blocks of the cluster in rank order, in block 0
-  if (cluster_size > 1) {
+  // add the blocks of the cluster in rank order, in block 0: the others put their sums into block 0's shared memory
+  // (stores through distributed shared memory: one way, no round trip), one cluster barrier makes them visible, and
+  // block 0 adds them in rank order, so the result does not depend on timing
+  if (cluster_size > 1 && MT <= 2) {
+    cg::cluster_group cluster = cg::this_cluster();
+    if (rank != 0) {
+      float* dst = cluster.map_shared_rank(&gathered[0][0][0][0], 0) + (size_t)(rank - 1) * RB * 16 * (COLS + 1);
+#pragma unroll 1
+      for (int e = tid; e < OUT_ELEMS; e += THREADS) {
+        const int r = e % 16, m = (e / 16) % COLS, b = e / (16 * COLS);
+        dst[(b * 16 + r) * (COLS + 1) + m] = part[b][r][m];  // each element is read and written by the same thread
+      }
+    }
+    cluster.sync();
+    if (rank != 0) return;
+#pragma unroll 1
+    for (int e = tid; e < OUT_ELEMS; e += THREADS) {
+      const int r = e % 16, m = (e / 16) % COLS, b = e / (16 * COLS);
+      float s = part[b][r][m];
+#pragma unroll
+      for (int k = 1; k < GSM_MAX_CLUSTER; ++k)
+        if (k < cluster_size) s += gathered[k - 1][b][r][m];
+      part[b][r][m] = s;
+    }
+  } else if (cluster_size > 1) {
+    // more than 16 batch rows: block 0 fetches the others' sums (a gathering buffer for them would not fit);
+    // the same additions in the same order
     cg::cluster_group cluster = cg::this_cluster();
     cluster.sync();
     if (rank == 0) {
@@ -297,20 +329,21 @@ gemm_small_m_kernel(const void* __restrict__ x_any, int ldx, const __nv_bfloat16
       for (int e = tid; e < OUT_ELEMS; e += THREADS) {
         const int r = e % 16, m = (e / 16) % COLS, b = e / (16 * COLS);
         const int at = (b * 16 + r) * (COLS + 1) + m;
-        float other[7];  // requested together (one round trip), added in rank order
+        float other[GSM_MAX_CLUSTER - 1];  // requested together (one round trip), added in rank order
 #pragma unroll
-        for (int k = 1; k < 8; ++k) other[k - 1] = k < cluster_size ? cluster.map_shared_rank(&part[0][0][0], k)[at] : 0.f;
+        for (int k = 1; k < GSM_MAX_CLUSTER; ++k) other[k - 1] = k < cluster_size ? cluster.map_shared_rank(&part[0][0][0], k)[at] : 0.f;
         float s = part[b][r][m];
 #pragma unroll
-        for (int k = 1; k < 8; ++k)
+        for (int k = 1; k < GSM_MAX_CLUSTER; ++k)
           if (k < cluster_size) s += other[k - 1];
-        part[b][r][m] = s;  // each element is read and written by the same thread
+        part[b][r][m] = s;
       }
     }
     cluster.sync();  // the other blocks' shared memory must live until block 0 has read it
     if (rank != 0) return;
   }
   __syncthreads();
+  MS_TIMELINE_MARK(3);
 
   if (EPI == GSM_EPI_RESADD) {
     // residual[m][n] += product, in place (each element belongs to one thread of one block); then the sum of
@@ -388,7 +421,7 @@ static GsmPlan gsm_plan(int blocks, int M, int K, int epi, int sm_count) {
   int want = (sm_count * 3 + blocks - 1) / blocks;
   int most = chunks / (2 * 8);  // at least two chunks per warp
   int cs = want < most ? want : most;
-  if (cs > 8) cs = 8;
+  if (cs > GSM_MAX_CLUSTER) cs = GSM_MAX_CLUSTER;  // (eight blocks a cluster spread a long row further but merged slower: measured)
   if (cs < 1) cs = 1;
   while (cs & (cs - 1)) cs &= cs - 1;  // a power of two
   const bool second_wave = blocks * cs > 3 * sm_count && blocks * cs <= 7 * sm_count;
@@ -412,7 +445,8 @@ static GsmPlan gsm_plan(int blocks, int M, int K, int epi, int sm_count) {
   p.sh.xs_chunks = fits ? xs_chunks : 0;
   // All blocks of the launch should be resident at once (a block of a second wave starts its copies only after
   // the wait): fewer chunks go through shared memory and more through registers if that is what it takes.
-  const size_t fixed = (fits ? (size_t)cols * stride * 2 : 0) + (size_t)(p.warps + p.rb) * 16 * (cols + 1) * 4 + 2048;
+  const size_t fixed = (fits ? (size_t)cols * stride * 2 : 0) +
+                       (size_t)(p.warps + p.rb + (cols <= 16 ? (GSM_MAX_CLUSTER - 1) * p.rb : p.rb)) * 16 * (cols + 1) * 4 + 2048;
   const int groups = (blocks + p.rb - 1) / p.rb;
   const int per_sm = (groups * cs + sm_count - 1) / sm_count;
   while (p.sh.staged > 1 && per_warp - (p.sh.staged - 1) <= GSM_HELD && per_sm <= 8 &&
@@ -491,6 +525,7 @@ static int gsm_dispatch(const void* x, int ldx, const void* w_lo, const void* w_
 #undef GSM_CASE
 }
 
+MS_TIMELINE_SETTER(ms_timeline_set_gemm_small_m)
 
 MS_API int ms_gemm_small_m_supports(int M, int N, int K) { return M >= 1 && M <= 64 && N >= 1 && K >= 8 && K % 8 == 0; }
 

@@ -24,13 +24,22 @@ class KernelError(RuntimeError):
 
 
 _lib = None
+_flavor = None
+
+
+def use_flavor(flavor) -> None:
+    """Chooses another build of the kernels (csrc/build.py FLAVORS) for this process; before the library is first used."""
+    global _flavor
+    if _lib is not None and flavor != _flavor:
+        raise KernelError("the kernel library is loaded already; choose the flavor before the first kernel call")
+    _flavor = flavor
 
 
 def lib():
     """The loaded kernel library (built on first use)."""
     global _lib
     if _lib is None:
-        path = _build.library_path()
+        path = _build.library_path(flavor=_flavor)
         try:
             L = ctypes.CDLL(str(path))
         except OSError as e:
@@ -51,7 +60,7 @@ def set_pdl(on: bool) -> None:
 
 
 def library_file() -> str:
-    return str(_build.library_path())
+    return str(_build.library_path(flavor=_flavor))
 
 
 class _Signatures:

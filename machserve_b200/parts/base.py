@@ -88,9 +88,14 @@ class Workspace:
         self._bufs: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
         self._retired: List[torch.Tensor] = []
         self._zeroed: set = set()  # buffers whose users rely on finding zeros (and leave zeros behind)
+        self._views: Dict[tuple, torch.Tensor] = {}  # (name, dtype, shape) -> the view handed out last time
 
     def get(self, name: str, shape, dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
         """A view of the buffer `name`; with `zero`, the buffer is zero-filled when it is made."""
+        shape = tuple(shape)
+        view = self._views.get((name, dtype, shape))
+        if view is not None:
+            return view  # asked for with every launch of every step: the same shape gets the same view
         n = 1
         for s in shape:
             n *= int(s)
@@ -103,7 +108,12 @@ class Workspace:
             self._bufs[key] = buf
             if zero:
                 self._zeroed.add(key)
-        return buf[:n].view(*shape)
+            for k in [k for k in self._views if k[0] == name and k[1] == dtype]:
+                del self._views[k]  # views of the buffer that was replaced
+        view = buf[:n].view(*shape)
+        if len(self._views) < 4096:
+            self._views[(name, dtype, shape)] = view
+        return view
 
     def rezero(self) -> None:
         """Zeros again what was handed out as zeros: after a kernel gave up half-way and may have left counters behind."""

@@ -52,3 +52,26 @@ def test_runner_and_engine_surface_it(model_root):
     with pytest.raises(RuntimeError, match="gave up a wait"):
         eng.generate([prompt], max_new_tokens=3)  # the engine checks when it runs empty
     assert ops.tc_status_codes() == (0, 0)
+
+
+def test_timeline_build_and_reader(model_root):
+    """The "timeline" build of the kernels and its reader: a decoding step of a tiny model leaves one record per
+    launch of a kernel that carries hooks, five per layer, in order, with the times in order."""
+    import json
+    import subprocess
+    import sys
+
+    from tests.helpers import REPO
+
+    d = make_model_dir(model_root, "D")  # 2 layers
+    r = subprocess.run([sys.executable, "-m", "machserve_b200.timeline", "--model", str(d), "--batch", "3", "--context", "40", "--json"],
+                       capture_output=True, text=True, timeout=600, cwd=str(REPO))
+    assert r.returncode == 0, r.stderr[-2000:]
+    recs = [json.loads(line) for line in r.stdout.splitlines() if line.startswith("{")]
+    kinds = [x["id"] for x in recs]
+    # first layer: plain QKV product after a norm kernel; then per layer attention, output product, gate/up, down product
+    assert kinds[:5] == [100, 200, 130, 121, 130] and kinds[5:10] == [101, 200, 130, 121, 130], kinds
+    for x in recs:
+        assert x["start"] <= x["wait_returned"] <= x["first_end"] <= x["last_end"]
+    for a, b in zip(recs, recs[1:]):
+        assert b["wait_returned"] >= a["last_end"] - 0.01  # a wait returns when the kernel before has ended
