@@ -496,3 +496,437 @@ MS_API int ms_gemm_tc_kn(const void* x, int ldx, const void* b, int ldb, float* 
   MS_LAUNCH_CHECK("gemm_tcgen05_kn");
   return 0;
 }
+
+// ================================================================================================
+// The product for few rows (decoding with up to 64 requests) the other way round: the WEIGHTS are the
+// 128-row operand of tcgen05.mma and the batch is its N = 16, 32 or 64, so a tile of 128 weight rows is
+// streamed once through a ring of TMA stages while the tensor core multiplies it with all batch rows:
+//
+//     acc[128 weight rows, NB batch rows] += W[n0 .. n0+127, k .. k+63] . x[0 .. NB-1, k .. k+63]^T
+//
+// The k range of a tile is split over the blocks of a thread-block cluster when there are few tiles.
+// Warp 0 (one thread) requests the weights of its first stages BEFORE it waits for the preceding kernel
+// of the stream (they do not depend on it) and the batch rows after; warp 1 (one thread) issues the
+// instructions; warps 2-5 take the accumulator out of tensor memory, thread = weight row.  Every block
+// then puts its sums for a share of the tile's rows into the shared memory of the block that owns that
+// share (distributed shared memory, stores only), one cluster barrier makes them visible, and the owner
+// adds them in rank order and runs the epilogue for its rows, so the result does not depend on timing:
+//   plain            out[m][n] (bfloat16 or float32), optionally divided by rms of residual row m
+//   SiLU-mul         a tile holds 64 gate rows and the 64 up rows of the same outputs
+//   residual add     residual[m][n] += product; sums of squares per row and block of 16 columns; bfloat16 copy
+// These are the epilogues of gemm_small_m.cu, whose products this kernel takes over where the matrices
+// are large or the rows more than 16.  Every mbarrier wait is bounded (code 4 producer, 5 issuer,
+// 6 epilogue for ms_gemm_tc_status).
+#include <cooperative_groups.h>
+
+#include "launch.cuh"
+
+namespace cg = cooperative_groups;
+
+#define RT_BM 128
+#define RT_BK 64
+#define RT_THREADS 192
+#define RT_W_BYTES (RT_BM * RT_BK * 2)
+#define RT_MAX_STAGES 8
+#define RT_MAX_CLUSTER 8
+
+enum { RT_EPI_BF16 = 0, RT_EPI_F32 = 1, RT_EPI_SILU_MUL = 2, RT_EPI_RESADD = 3 };
+
+struct RtExtra {
+  const float* stats_in;  // row scaling: sums of squares [M][stats_in_nb] of the rows the activations were rounded from
+  int stats_in_nb;
+  float eps;
+  int scale_k;            // the width of those rows (the mean of squares is over it)
+  float* residual;        // residual epilogue: float32 [M][ldr], added into in place
+  int ldr;
+  float* stats_out;       // [M][ceil(N / 16)]
+  __nv_bfloat16* copy_out;  // optional: the new residual rounded, [M][ldc]
+  int ldc;
+};
+
+struct RtShared {
+  unsigned long long full[RT_MAX_STAGES];
+  unsigned long long empty[RT_MAX_STAGES];
+  unsigned long long done;
+  unsigned tmem_base;
+  int abort_flag;
+  float inv_rms[64];
+};
+
+__device__ __forceinline__ void rt_ld16(unsigned taddr, float (&v)[16]) {
+  unsigned r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared memory: [stages x (W tile 16 KB | x tile NB x 128 B)] [gather: RT_BM rows x (NB + 1) floats] [RtShared].
+// The gathering buffer holds, for the rows this block owns, every cluster block's sums: [rank][row of the share][NB + 1].
+template <int NB, int EPI, int SCALE>
+__global__ void __launch_bounds__(RT_THREADS, 2)
+gemm_rows_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
+                    const __grid_constant__ CUtensorMap map_x, void* __restrict__ out, int ldo, int M, int N, int K,
+                    int cluster_size, int stages, RtExtra ex) {
+  constexpr int X_BYTES = NB * RT_BK * 2;
+  constexpr int STAGE_BYTES = RT_W_BYTES + X_BYTES;
+  constexpr int GROW = NB + 4;  // floats per gathered row: 16-byte rows whose quarter-warps fall into different banks
+  constexpr int TMEM_COLS = NB < 32 ? 32 : NB;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  float* gather = reinterpret_cast<float*>(tiles + (size_t)stages * STAGE_BYTES);  // (only with a cluster)
+  RtShared* sh = reinterpret_cast<RtShared*>(gather + (cluster_size > 1 ? RT_BM * GROW : 0));
+  volatile int* abort_flag = &sh->abort_flag;
+
+  ms_pdl_trigger();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x / cluster_size, rank = blockIdx.x - tile * cluster_size;
+  // the tile's weight rows: 128 consecutive ones, or 64 gate rows and the 64 up rows of the same outputs
+  const int n0 = tile * (EPI == RT_EPI_SILU_MUL ? 64 : RT_BM);
+  const int kt_count = (K + RT_BK - 1) / RT_BK;
+  const int kt_per = (kt_count + cluster_size - 1) / cluster_size;
+  const int kt0 = rank * kt_per;
+  const int my_kt = max(0, min(kt_count, kt0 + kt_per) - kt0);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      tc_mbar_init(tc_smem(&sh->full[s]), 1);
+      tc_mbar_init(tc_smem(&sh->empty[s]), 1);
+    }
+    tc_mbar_init(tc_smem(&sh->done), 1);
+    sh->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem(&sh->tmem_base)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem = sh->tmem_base;
+
+  if (warp == 0 && lane == 0) {
+    // producer.  The weights of the first stages go out before the wait for the preceding kernel; the batch rows,
+    // which it wrote, after.  A stage's barrier counts the bytes of both.
+    const int first = my_kt < stages ? my_kt : stages;
+    for (int kt = 0; kt < first; ++kt) {
+      const unsigned dst = tc_smem(tiles + kt * STAGE_BYTES), bar = tc_smem(&sh->full[kt]);
+      tc_mbar_expect_tx(bar, STAGE_BYTES);
+      if (EPI == RT_EPI_SILU_MUL) {
+        tc_tma_load_2d(dst, &map_w, (kt0 + kt) * RT_BK, n0, bar);
+        tc_tma_load_2d(dst + 64 * RT_BK * 2, &map_w2, (kt0 + kt) * RT_BK, n0, bar);
+      } else {
+        tc_tma_load_2d(dst, &map_w, (kt0 + kt) * RT_BK, n0, bar);
+        tc_tma_load_2d(dst + 64 * RT_BK * 2, &map_w, (kt0 + kt) * RT_BK, n0 + 64, bar);
+      }
+    }
+    ms_pdl_wait();
+    for (int kt = 0; kt < first; ++kt)
+      tc_tma_load_2d(tc_smem(tiles + kt * STAGE_BYTES + RT_W_BYTES), &map_x, (kt0 + kt) * RT_BK, 0, tc_smem(&sh->full[kt]));
+    for (int kt = first; kt < my_kt; ++kt) {
+      const int s = kt % stages;
+      if (!tc_mbar_wait(tc_smem(&sh->empty[s]), ((kt / stages) - 1) & 1, abort_flag, 4)) break;
+      const unsigned dst = tc_smem(tiles + s * STAGE_BYTES), bar = tc_smem(&sh->full[s]);
+      tc_mbar_expect_tx(bar, STAGE_BYTES);
+      if (EPI == RT_EPI_SILU_MUL) {
+        tc_tma_load_2d(dst, &map_w, (kt0 + kt) * RT_BK, n0, bar);
+        tc_tma_load_2d(dst + 64 * RT_BK * 2, &map_w2, (kt0 + kt) * RT_BK, n0, bar);
+      } else {
+        tc_tma_load_2d(dst, &map_w, (kt0 + kt) * RT_BK, n0, bar);
+        tc_tma_load_2d(dst + 64 * RT_BK * 2, &map_w, (kt0 + kt) * RT_BK, n0 + 64, bar);
+      }
+      tc_tma_load_2d(dst + RT_W_BYTES, &map_x, (kt0 + kt) * RT_BK, 0, bar);
+    }
+  } else if (warp == 1 && lane == 0) {
+    // issuer: four K = 16 instructions per stage, then the stage goes back to the producer
+    const unsigned idesc = tc_instr_desc(RT_BM, NB);
+    bool ok = true;
+    for (int kt = 0; kt < my_kt && ok; ++kt) {
+      const int s = kt % stages;
+      ok = tc_mbar_wait(tc_smem(&sh->full[s]), (kt / stages) & 1, abort_flag, 5);
+      if (!ok) break;
+      tc_fence_after();
+      const unsigned a_src = tc_smem(tiles + s * STAGE_BYTES);
+      const unsigned b_src = a_src + RT_W_BYTES;
+#pragma unroll
+      for (int k = 0; k < RT_BK / 16; ++k)
+        tc_mma(tmem, tc_smem_desc(a_src + k * 32), tc_smem_desc(b_src + k * 32), idesc, (kt | k) != 0);
+      tc_commit(tc_smem(&sh->empty[s]));
+    }
+    if (ok && my_kt > 0) tc_commit(tc_smem(&sh->done));
+  } else if (warp >= 2) {
+    // epilogue: the row scaling's 1 / rms first (it needs only what the preceding kernel left)
+    ms_pdl_wait();
+    const int et = threadIdx.x - 64;  // 0..127
+    if (SCALE == 1) {
+      if (et < NB) {
+        float ss = 0.f;
+        if (et < M)
+          for (int b = 0; b < ex.stats_in_nb; ++b) ss += ex.stats_in[(size_t)et * ex.stats_in_nb + b];
+        sh->inv_rms[et] = rsqrtf(ss / (float)ex.scale_k + ex.eps);
+      }
+      asm volatile("bar.sync 1, 128;\n" ::: "memory");
+    }
+    const bool have = my_kt == 0 || tc_mbar_wait(tc_smem(&sh->done), 0, abort_flag, 6);
+    const int group = warp & 3;
+    const int row = group * 32 + lane;  // the accumulator lane = weight row of the tile
+    const unsigned row_addr = tmem + ((unsigned)(group * 32) << 16);
+    if (have) tc_fence_after();
+    if (cluster_size == 1) {
+      // one block has the whole k range: straight from tensor memory to the output, 16 batch rows at a time; a warp's
+      // lanes are 32 consecutive outputs of a batch row
+      float* up_s = reinterpret_cast<float*>(tiles);  // gated form: the up rows' values for the gate rows' threads
+      if (EPI == RT_EPI_SILU_MUL) {                    // (the stages are free: every product has been done)
+        if (have && row >= 64) {
+#pragma unroll
+          for (int c = 0; c < NB; c += 16) {
+            float v[16];
+            rt_ld16(row_addr + c, v);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) up_s[(row - 64) * GROW + c + j] = v[j];
+          }
+        }
+        asm volatile("bar.sync 1, 128;\n" ::: "memory");
+      }
+      const int n = n0 + (EPI == RT_EPI_SILU_MUL ? (row & 63) : row);
+      if (have && !(EPI == RT_EPI_SILU_MUL && row >= 64)) {
+#pragma unroll
+        for (int c = 0; c < NB; c += 16) {
+          float v[16];
+          if (my_kt > 0) {
+            rt_ld16(row_addr + c, v);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = 0.f;
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = c + j;
+            const bool ok = m < M && n < N;
+            const float rs = SCALE == 1 ? sh->inv_rms[m] : 1.f;
+            if (EPI == RT_EPI_SILU_MUL) {
+              const float gate = v[j] * rs, up = up_s[row * GROW + m] * rs;
+              if (ok) reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + n] = __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
+            } else if (EPI == RT_EPI_RESADD) {
+              float r = 0.f;
+              if (ok) {
+                r = ex.residual[(size_t)m * ex.ldr + n] + v[j];
+                ex.residual[(size_t)m * ex.ldr + n] = r;
+                if (ex.copy_out) ex.copy_out[(size_t)m * ex.ldc + n] = __float2bfloat16_rn(r);
+              }
+              float ss = r * r;  // the sum of squares of 16 consecutive columns: 16 consecutive lanes
+#pragma unroll
+              for (int off = 8; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off, 16);
+              if ((lane & 15) == 0 && ok) ex.stats_out[(size_t)m * ((N + 15) / 16) + n / 16] = ss;
+            } else if (ok) {
+              if (EPI == RT_EPI_F32)
+                reinterpret_cast<float*>(out)[(size_t)m * ldo + n] = v[j] * rs;
+              else
+                reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + n] = __float2bfloat16_rn(v[j] * rs);
+            }
+          }
+        }
+      }
+    } else if (have) {
+      // the k range is split over a cluster: this block's sums go to the blocks that own the rows.  The rows are
+      // shared out in runs: run `owner` belongs to the cluster's block `owner`.  The gated form pairs gate row i with
+      // up row 64 + i, so both halves are cut alike.
+      const int half = EPI == RT_EPI_SILU_MUL ? 64 : RT_BM;
+      const int run = half / cluster_size;
+      const int i = EPI == RT_EPI_SILU_MUL ? (row & 63) : row;
+      const int owner = i / run;
+      const int local = (i - owner * run) + ((EPI == RT_EPI_SILU_MUL && row >= 64) ? run : 0);
+      cg::cluster_group cluster = cg::this_cluster();
+      const int rows_owned = EPI == RT_EPI_SILU_MUL ? 2 * run : run;
+      float* dst = cluster.map_shared_rank(gather, owner) + ((size_t)rank * rows_owned + local) * GROW;
+#pragma unroll
+      for (int c = 0; c < NB; c += 16) {
+        float v[16];
+        if (my_kt > 0) {
+          rt_ld16(row_addr + c, v);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(dst + c + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      }
+    }
+  }
+  tc_fence_before();
+  if (cluster_size > 1) {
+    cg::this_cluster().sync();
+  } else {
+    __syncthreads();
+  }
+  if (cluster_size > 1 && warp >= 2 && !*abort_flag) {
+    // the rows this block owns, summed over the cluster's blocks in rank order
+    const int et = threadIdx.x - 64;
+    const int half = EPI == RT_EPI_SILU_MUL ? 64 : RT_BM;
+    const int run = half / cluster_size;
+    const int rows_owned = EPI == RT_EPI_SILU_MUL ? 2 * run : run;
+    const int first = n0 + rank * run;  // the first output column (weight row) of this block's run
+    for (int e = et; e < run * NB; e += 128) {
+      const int m = e / run, i = e - m * run;  // consecutive threads: consecutive outputs of one batch row
+      float a = 0.f, b = 0.f;
+      for (int k = 0; k < cluster_size; ++k) {
+        a += gather[((size_t)k * rows_owned + i) * GROW + m];
+        if (EPI == RT_EPI_SILU_MUL) b += gather[((size_t)k * rows_owned + run + i) * GROW + m];
+      }
+      const int n = first + i;
+      const bool ok = m < M && n < N;
+      const float rs = SCALE == 1 ? sh->inv_rms[m] : 1.f;
+      if (EPI == RT_EPI_SILU_MUL) {
+        const float gate = a * rs, up = b * rs;
+        if (ok) reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + n] = __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
+      } else if (EPI == RT_EPI_RESADD) {
+        float v = 0.f;
+        if (ok) {
+          v = ex.residual[(size_t)m * ex.ldr + n] + a;
+          ex.residual[(size_t)m * ex.ldr + n] = v;
+          if (ex.copy_out) ex.copy_out[(size_t)m * ex.ldc + n] = __float2bfloat16_rn(v);
+        }
+        // the sum of squares of each 16 consecutive columns of a row: 16 consecutive lanes (a run is a multiple of 16)
+        float ss = v * v;
+#pragma unroll
+        for (int off = 8; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off, 16);
+        if ((lane & 15) == 0 && ok) ex.stats_out[(size_t)m * ((N + 15) / 16) + n / 16] = ss;
+      } else if (ok) {
+        if (EPI == RT_EPI_F32)
+          reinterpret_cast<float*>(out)[(size_t)m * ldo + n] = a * rs;
+        else
+          reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + n] = __float2bfloat16_rn(a * rs);
+      }
+    }
+  }
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------ host
+
+struct RtPlan {
+  int nb, cluster, stages;
+  size_t smem;
+};
+
+// How a product is spread over the GPU: tiles of 128 weight rows (64 outputs of the gated form), the k range of a
+// tile split over a cluster while that leaves every block at least two steps of 64 and all blocks resident at once
+// (two blocks per SM), and as many stages as the block's share of an SM's shared memory holds.
+static RtPlan rt_plan(int M, int tiles, int K, int sm_count) {
+  RtPlan p;
+  p.nb = M <= 16 ? 16 : M <= 32 ? 32 : 64;
+  const int kt = (K + RT_BK - 1) / RT_BK;
+  p.cluster = 1;
+  while (p.cluster * 2 <= RT_MAX_CLUSTER && (long long)tiles * p.cluster * 2 <= 2LL * sm_count && kt / (p.cluster * 2) >= 2) p.cluster *= 2;
+  const int per = (kt + p.cluster - 1) / p.cluster;
+  const size_t stage = RT_W_BYTES + (size_t)p.nb * RT_BK * 2;
+  const size_t fixed = (p.cluster > 1 ? (size_t)RT_BM * (p.nb + 4) * sizeof(float) : 0) + sizeof(RtShared) + 1024;
+  const size_t budget = ((long long)tiles * p.cluster <= sm_count ? 200 : 104) * 1024;
+  int stages = (int)((budget - fixed) / stage);
+  if (stages > per) stages = per;
+  if (stages > RT_MAX_STAGES) stages = RT_MAX_STAGES;
+  if (stages < 1) stages = 1;
+  p.stages = stages;
+  p.smem = (size_t)stages * stage + fixed;
+  return p;
+}
+
+template <int NB, int EPI, int SCALE>
+static int rt_launch_nb(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx, void* out, int ldo, int M, int N,
+                        int K, int tiles, const RtPlan& p, const RtExtra& ex, cudaStream_t stream) {
+  auto kern = gemm_rows_tc_kernel<NB, EPI, SCALE>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024);
+    if (e != cudaSuccess) {
+      ms_set_error("gemm_rows_tc: cannot configure shared memory: %s", cudaGetErrorString(e));
+      return 2;
+    }
+    configured = true;
+  }
+  MS_LAUNCH_RESULT("gemm_rows_tc", ms_launch(kern, dim3(tiles * p.cluster), dim3(RT_THREADS), p.smem, stream, p.cluster, true, mw, mw2,
+                                            mx, out, ldo, M, N, K, p.cluster, p.stages, ex));
+  return 0;
+}
+
+template <int EPI, int SCALE>
+static int rt_launch(const void* x, int ldx, const void* w, const void* w2, void* out, int ldo, int M, int N, int K,
+                     const RtExtra& ex, int sm_count, cudaStream_t stream) {
+  MS_REQUIRE(M >= 1 && M <= 64 && N >= 1 && K >= 8 && K % 8 == 0, "gemm_rows_tc: M=%d (1..64), N=%d, K=%d (a multiple of 8) is not covered", M, N, K);
+  MS_REQUIRE(ldx % 8 == 0 && ldx >= K && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0) && ((uintptr_t)w2 % 16 == 0),
+             "gemm_rows_tc: operands must be 16-byte aligned with row strides that are multiples of 8");
+  const int tiles = EPI == RT_EPI_SILU_MUL ? (N + 63) / 64 : (N + RT_BM - 1) / RT_BM;
+  const RtPlan p = rt_plan(M, tiles, K, sm_count);
+  CUtensorMap mw, mw2, mx;
+  if (int rc = tc_make_map(&mw, w, N, K, K, 64)) return rc;
+  if (int rc = tc_make_map(&mw2, w2 ? w2 : w, N, K, K, 64)) return rc;
+  if (int rc = tc_make_map(&mx, x, M, K, ldx, p.nb)) return rc;
+  if (p.nb == 16) return rt_launch_nb<16, EPI, SCALE>(mw, mw2, mx, out, ldo, M, N, K, tiles, p, ex, stream);
+  if (p.nb == 32) return rt_launch_nb<32, EPI, SCALE>(mw, mw2, mx, out, ldo, M, N, K, tiles, p, ex, stream);
+  return rt_launch_nb<64, EPI, SCALE>(mw, mw2, mx, out, ldo, M, N, K, tiles, p, ex, stream);
+}
+
+MS_API int ms_gemm_rows_tc_supports(int M, int N, int K) { return M >= 1 && M <= 64 && N >= 1 && K >= 8 && K % 8 == 0; }
+
+// out[M, N] = x[M, K] . w[N, K]^T for M <= 64; out bfloat16 or float32.
+MS_API int ms_gemm_rows_tc(const void* x, int ldx, const void* w, void* out, int out_dtype, int ldo, int M, int N, int K,
+                           int sm_count, cudaStream_t stream) {
+  if (M == 0) return 0;
+  MS_REQUIRE(ldo >= N, "gemm_rows_tc: out row stride %d is shorter than N = %d", ldo, N);
+  if (out_dtype == MS_F32) return rt_launch<RT_EPI_F32, 0>(x, ldx, w, nullptr, out, ldo, M, N, K, RtExtra{}, sm_count, stream);
+  MS_REQUIRE(out_dtype == MS_BF16, "gemm_rows_tc: unknown out dtype %d", out_dtype);
+  return rt_launch<RT_EPI_BF16, 0>(x, ldx, w, nullptr, out, ldo, M, N, K, RtExtra{}, sm_count, stream);
+}
+
+// out[M, I] = silu(x . w_gate^T) * (x . w_up^T); w_gate, w_up [I, K]; out bfloat16.
+MS_API int ms_gemm_rows_tc_silu_mul(const void* x, int ldx, const void* w_gate, const void* w_up, void* out, int ldo, int M,
+                                    int I, int K, int sm_count, cudaStream_t stream) {
+  if (M == 0) return 0;
+  MS_REQUIRE(ldo >= I && w_up != nullptr, "gemm_rows_tc_silu_mul: bad arguments");
+  return rt_launch<RT_EPI_SILU_MUL, 0>(x, ldx, w_gate, w_up, out, ldo, M, I, K, RtExtra{}, sm_count, stream);
+}
+
+// out = (x . w^T) / rms(row), or silu(. / rms) * (. / rms) with w_up: x is the residual rounded to bfloat16 [M, K],
+// stats_in [M][stats_nb] the sums of squares of its rows (see ms_gemm_rows_tc_resadd).  out bfloat16.
+MS_API int ms_gemm_rows_tc_scaled(const void* x, int ldx, const float* stats_in, int stats_nb, float eps, const void* w,
+                                  const void* w_up, void* out, int ldo, int M, int N, int K, int sm_count, cudaStream_t stream) {
+  if (M == 0) return 0;
+  MS_REQUIRE(ldo >= N && stats_in != nullptr && stats_nb >= 1, "gemm_rows_tc_scaled: bad arguments");
+  RtExtra ex = {};
+  ex.stats_in = stats_in;
+  ex.stats_in_nb = stats_nb;
+  ex.eps = eps;
+  ex.scale_k = K;
+  if (w_up) return rt_launch<RT_EPI_SILU_MUL, 1>(x, ldx, w, w_up, out, ldo, M, N, K, ex, sm_count, stream);
+  return rt_launch<RT_EPI_BF16, 1>(x, ldx, w, nullptr, out, ldo, M, N, K, ex, sm_count, stream);
+}
+
+// residual[M, N] += x[M, K] . w[N, K]^T in place (float32); stats_out[m][b] = the sum of squares of the new residual's
+// row m over columns [16 b, 16 b + 16); copy_out (optional, bfloat16 [M][ldc]) = the new residual rounded.
+MS_API int ms_gemm_rows_tc_resadd(const void* x, int ldx, const void* w, float* residual, int ldr, float* stats_out,
+                                  void* copy_out, int ldc, int M, int N, int K, int sm_count, cudaStream_t stream) {
+  if (M == 0) return 0;
+  MS_REQUIRE(residual != nullptr && stats_out != nullptr && ldr >= N && (copy_out == nullptr || ldc >= N), "gemm_rows_tc_resadd: bad arguments");
+  RtExtra ex = {};
+  ex.residual = residual;
+  ex.ldr = ldr;
+  ex.stats_out = stats_out;
+  ex.copy_out = (__nv_bfloat16*)copy_out;
+  ex.ldc = ldc;
+  return rt_launch<RT_EPI_RESADD, 0>(x, ldx, w, nullptr, nullptr, 0, M, N, K, ex, sm_count, stream);
+}

@@ -83,6 +83,10 @@ class _Signatures:
     ms_gemm_small_m_scaled = [P, I, P, I, F, P, P, P, I, I, I, I, I, P]
     ms_gemm_tc = [P, I, P, P, I, I, I, I, I, P]
     ms_gemm_tc_silu_mul = [P, I, P, P, I, I, I, I, P]
+    ms_gemm_rows_tc = [P, I, P, P, I, I, I, I, I, I, P]
+    ms_gemm_rows_tc_silu_mul = [P, I, P, P, P, I, I, I, I, I, P]
+    ms_gemm_rows_tc_scaled = [P, I, P, I, F, P, P, P, I, I, I, I, I, P]
+    ms_gemm_rows_tc_resadd = [P, I, P, P, I, P, P, I, I, I, I, I, P]
     ms_gemm_tc_wait_probe = [I, P]
     ms_attention_tc_wait_probe = [I, P]
     ms_take_sampled_tokens = [P, P, P, I, I, P]
@@ -570,6 +574,71 @@ def gemm_tc_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor
     _need(x.stride(1) == 1 and out.stride(1) == 1 and tuple(out.shape) == (m, i), "gemm_tc_silu_mul: bad layout")
     _check(lib().ms_gemm_tc_silu_mul(_ptr(x), x.stride(0), _ptr(w_gate_up), _ptr(out), out.stride(0), m, i, k, _stream()),
            "gemm_tc_silu_mul")
+    return out
+
+
+def gemm_rows_tc_supports(m: int, n: int, k: int) -> bool:
+    """Up to 64 rows, K in steps of 8."""
+    return 1 <= m <= 64 and n >= 1 and k >= 8 and k % 8 == 0
+
+
+def gemm_rows_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[M, N] = x[M, K] . w[N, K]^T for M <= 64 on tcgen05 tensor cores with the weights as the 128-row operand,
+    streamed once through TMA stages; bfloat16 operands, bfloat16 or float32 out."""
+    m, k = x.shape
+    n = w.shape[0]
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "gemm_rows_tc: operands must be bfloat16")
+    _need(w.is_contiguous() and w.shape[1] == k and x.stride(1) == 1 and out.stride(1) == 1, "gemm_rows_tc: bad layout")
+    _need(tuple(out.shape) == (m, n), "gemm_rows_tc: bad output shape")
+    _check(lib().ms_gemm_rows_tc(_ptr(x), x.stride(0), _ptr(w), _ptr(out), _code(out), out.stride(0), m, n, k, sm_count(), _stream()),
+           "gemm_rows_tc")
+    return out
+
+
+def gemm_rows_tc_silu_mul(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[M, I] = silu(x . w_gate^T) * (x . w_up^T) for M <= 64, all bfloat16, in one kernel."""
+    m, k = x.shape
+    i = w_gate.shape[0]
+    _need(x.dtype == w_gate.dtype == w_up.dtype == out.dtype == torch.bfloat16, "gemm_rows_tc_silu_mul: bfloat16 only")
+    _need(w_gate.is_contiguous() and w_up.is_contiguous() and tuple(w_up.shape) == (i, k) and w_gate.shape[1] == k,
+          "gemm_rows_tc_silu_mul: bad weights")
+    _need(x.stride(1) == 1 and out.stride(1) == 1 and tuple(out.shape) == (m, i), "gemm_rows_tc_silu_mul: bad layout")
+    _check(lib().ms_gemm_rows_tc_silu_mul(_ptr(x), x.stride(0), _ptr(w_gate), _ptr(w_up), _ptr(out), out.stride(0), m, i, k,
+                                          sm_count(), _stream()), "gemm_rows_tc_silu_mul")
+    return out
+
+
+def gemm_rows_tc_resadd(x, w, residual, stats_out, copy_out=None):
+    """As gemm_small_m_resadd, for up to 64 rows: residual += x . w^T (float32, in place), the sums of squares of the
+    new residual per row and block of 16 columns, and optionally its bfloat16 copy."""
+    m, k = x.shape
+    n = w.shape[0]
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and residual.dtype == torch.float32, "gemm_rows_tc_resadd: bad dtypes")
+    _need(w.is_contiguous() and w.shape[1] == k and x.stride(1) == 1 and residual.stride(1) == 1, "gemm_rows_tc_resadd: bad layout")
+    _need(tuple(residual.shape) == (m, n), "gemm_rows_tc_resadd: the residual must be [rows, N]")
+    _need(stats_out.dtype == torch.float32 and stats_out.is_contiguous() and stats_out.numel() >= m * gemm_small_m_stats_blocks(n),
+          "gemm_rows_tc_resadd: bad stats buffer")
+    _need(copy_out is None or (copy_out.dtype == torch.bfloat16 and tuple(copy_out.shape) == (m, n) and copy_out.stride(1) == 1),
+          "gemm_rows_tc_resadd: the copy must be bfloat16 [rows, N]")
+    _check(lib().ms_gemm_rows_tc_resadd(_ptr(x), x.stride(0), _ptr(w), _ptr(residual), residual.stride(0), _ptr(stats_out),
+                                        _ptr(copy_out), copy_out.stride(0) if copy_out is not None else 0, m, n, k, sm_count(),
+                                        _stream()), "gemm_rows_tc_resadd")
+    return residual
+
+
+def gemm_rows_tc_scaled(x, stats, stats_blocks, eps, w, w_up, out):
+    """As gemm_small_m_scaled, for up to 64 rows: out = (x . w^T) / rms(row), or the gated form with w_up."""
+    m, k = x.shape
+    n = w.shape[0]
+    _need(x.dtype == torch.bfloat16 and stats.dtype == torch.float32 and w.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
+          "gemm_rows_tc_scaled: bad dtypes")
+    _need(w.is_contiguous() and w.shape[1] == k, "gemm_rows_tc_scaled: bad weights")
+    _need(w_up is None or (w_up.dtype == torch.bfloat16 and w_up.is_contiguous() and tuple(w_up.shape) == (n, k)),
+          "gemm_rows_tc_scaled: bad up weights")
+    _need(x.stride(1) == 1 and out.stride(1) == 1 and tuple(out.shape) == (m, n), "gemm_rows_tc_scaled: bad layout")
+    _need(stats.is_contiguous() and stats.numel() >= m * stats_blocks, "gemm_rows_tc_scaled: bad stats buffer")
+    _check(lib().ms_gemm_rows_tc_scaled(_ptr(x), x.stride(0), _ptr(stats), int(stats_blocks), float(eps), _ptr(w), _ptr(w_up),
+                                        _ptr(out), out.stride(0), m, n, k, sm_count(), _stream()), "gemm_rows_tc_scaled")
     return out
 
 
