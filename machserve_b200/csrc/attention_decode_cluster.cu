@@ -123,8 +123,12 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
   const size_t head_off = (size_t)kvh * page_size * HD;
 
   const int n_my = my_hi - my_lo + 1;
+  // A run of keys that the stages hold at once is requested whole, before the wait.  A longer run goes through the
+  // stages in two halves: while the warps attend to the tiles of one half, the copies of the next round fill the other.
+  const bool pipelined = n_my > stages && stages >= 2;
+  const int per_round = pipelined ? stages / 2 : stages;
   // the first round of tiles, without the current position's row
-  dcl_load_round<HD, DCL_THREADS>(kv_s, k_pages, v_pages, table, num_pages, page_size, page_elems, head_off, my_lo, min(stages, max(n_my, 0)),
+  dcl_load_round<HD, DCL_THREADS>(kv_s, k_pages, v_pages, table, num_pages, page_size, page_elems, head_off, my_lo, min(per_round, max(n_my, 0)),
                      first_key, pos, pos, tid);
 
   ms_pdl_wait();
@@ -151,7 +155,7 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
         const int page = table[pos / page_size];
         page_ok = page >= 0 && page < num_pages;
         cache_off = (size_t)(page_ok ? page : 0) * page_elems + head_off + (size_t)(pos % page_size) * HD;
-        if (ptile - my_lo < stages)  // else the tile is copied from the cache in a later round, after a barrier
+        if (ptile - my_lo < per_round)  // else the tile is copied from the cache in a later round, after a barrier
           tile_row = kv_s + (size_t)(ptile - my_lo) * 2 * TILE_ELEMS + (pos - ptile * DCL_TILE) * STRIDE;
       }
       // heads 0 .. groups-1: the group's query heads; then (mine) the key head and the value head
@@ -217,7 +221,7 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
   }
   // the current position's own key and value, if its tile is in the first round
   {
-    if (!row_done && live && ptile >= my_lo && ptile <= my_hi && ptile - my_lo < stages && tid < 2 * (HD / 8)) {
+    if (!row_done && live && ptile >= my_lo && ptile <= my_hi && ptile - my_lo < per_round && tid < 2 * (HD / 8)) {
       const int which = tid / (HD / 8), ch = tid - which * (HD / 8);
       const int page = table[pos / page_size];
       const bool ok = page >= 0 && page < num_pages;
@@ -234,17 +238,26 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
   st.init();
   unsigned qa[HD / 16][4];
   const int lo[2] = {first_key, first_key}, hi[2] = {pos, pos};
-  // Rounds of up to `stages` tiles; within a round warp w takes the tiles w, w + 4, ..., each whole: 64 keys in
-  // one step of the online softmax.  (Few blocks hold their whole run in one round, requested before the wait.)
+  // Rounds of up to `per_round` tiles; within a round warp w takes the parts w, w + DCL_WARPS, ... of the round's tiles.
+  if (pipelined) {
+    __syncthreads();  // the current position's key and value are in the cache before a later round is copied from it
+    dcl_load_round<HD, DCL_THREADS>(kv_s + (size_t)per_round * 2 * TILE_ELEMS, k_pages, v_pages, table, num_pages, page_size, page_elems,
+                                    head_off, my_lo + per_round, min(per_round, n_my - per_round), first_key, pos, -1, tid);
+  }
 #pragma unroll 1
-  for (int r0 = 0; r0 < n_my; r0 += stages) {
-    const int nr = min(stages, n_my - r0);
-    if (r0 > 0) {
+  for (int r0 = 0, round = 0; r0 < n_my; r0 += per_round, ++round) {
+    const int nr = min(per_round, n_my - r0);
+    __nv_bfloat16* buf = kv_s + (pipelined && (round & 1) ? (size_t)per_round * 2 * TILE_ELEMS : 0);
+    if (!pipelined && r0 > 0) {
       __syncthreads();  // every warp is done with the stages
       dcl_load_round<HD, DCL_THREADS>(kv_s, k_pages, v_pages, table, num_pages, page_size, page_elems, head_off, my_lo + r0, nr, first_key,
                          pos, -1, tid);
     }
-    ms_cp_async_wait<0>();
+    if (pipelined) {
+      ms_cp_async_wait<1>();  // this round's copies have landed; the next round's may still be on their way
+    } else {
+      ms_cp_async_wait<0>();
+    }
     __syncthreads();
     if (r0 == 0) {
       const int mat = lane >> 3, within = lane & 7;
@@ -257,11 +270,18 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
 #pragma unroll 1
     for (int sl = warp; sl < nr * PARTS; sl += DCL_WARPS) {
       const int i = sl / PARTS, krow = (sl % PARTS) * KPW;
-      const __nv_bfloat16* ks = kv_s + (size_t)i * 2 * TILE_ELEMS;
+      const __nv_bfloat16* ks = buf + (size_t)i * 2 * TILE_ELEMS;
       ms_attend_keys<HD, KPW / 16, true>(st, qa, ks, ks + TILE_ELEMS, krow, (my_lo + r0 + i) * DCL_TILE + krow, lo, hi, first_key,
                                          pos, scale_log2, lane);
     }
+    if (pipelined) {
+      __syncthreads();  // every warp is done with this half: the round after the next goes there (an empty
+      const int nx = r0 + 2 * per_round;  // request keeps the count of copy groups in step)
+      dcl_load_round<HD, DCL_THREADS>(buf, k_pages, v_pages, table, num_pages, page_size, page_elems, head_off, my_lo + nx,
+                                      max(0, min(per_round, n_my - nx)), first_key, pos, -1, tid);
+    }
   }
+  ms_cp_async_wait<0>();
   __syncthreads();  // the stages are used for the merge next
   MS_TIMELINE_MARK(1);
 
@@ -372,6 +392,8 @@ static int launch_decode_cluster_k(const void* q, DclRaw raw, const void* k_page
   static size_t configured = 0;  // per instantiation: the largest size asked for so far
   if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    // the largest shared-memory share of an SM, so that as many blocks as fit are resident at once
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     if (e != cudaSuccess) {
       ms_set_error("attention_decode_cluster: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
       return 2;
@@ -417,7 +439,7 @@ static int launch_decode_cluster(const void* q, DclRaw raw, const void* k_pages,
   return launch_decode_cluster_k<HD, FUSED, KPW, WARPS>(q, raw, k_pages, v_pages, out, rows, positions, slot_of_token,   \
                                                         block_table, max_pages, num_pages, tokens, hq, hkv, page_size,   \
                                                         window, scale, num_splits, stages, stream)
-  if (stages * 2 <= 4) MS_DCL_LAUNCH(32, 4);
+  if (stages <= 4 && warps == 4) MS_DCL_LAUNCH(32, 4);  // few tiles a round: half a tile per warp keeps all four busy
   if (warps == 8) MS_DCL_LAUNCH(32, 8);
   MS_DCL_LAUNCH(64, 4);
 #undef MS_DCL_LAUNCH
