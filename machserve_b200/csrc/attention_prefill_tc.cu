@@ -317,7 +317,7 @@ attention_prefill_tc_single_kernel(const __grid_constant__ CUtensorMap map_q, co
                             const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
                             const int* __restrict__ positions, const int* __restrict__ slot_of_token,
                             const int* __restrict__ block_table, int max_pages, int num_pages, int hq, int hkv,
-                            int page_size, int window, float scale_log2, float* __restrict__ scratch,
+                            int page_size, int window, float scale_log2, int num_runs, float* __restrict__ scratch,
                             int* __restrict__ counters) {
   constexpr int PANELS = HD / 64;          // 64-column panels of Q, K and V
   constexpr int PANEL_BYTES = 128 * 128;   // 128 rows of 128 bytes
@@ -330,9 +330,12 @@ attention_prefill_tc_single_kernel(const __grid_constant__ CUtensorMap map_q, co
   unsigned char* k_s = v_s + 2 * KV_BYTES;   // one stage
   volatile int* abort_flag = &sh->abort_flag;
 
-  const int tile_id = gridDim.x - 1 - blockIdx.x;  // the longest tiles first
+  // blocks are handed out in the order of blockIdx.x, then .y: the heads of the last tile's first run of keys, the
+  // heads of its second run, ..., then the tile before it: the longest rows of key tiles first, their runs together
+  const int nruns = num_runs;
+  const int tile_id = (int)(gridDim.y / nruns) - 1 - (int)(blockIdx.y / nruns);
   const int row0 = tile_row0[tile_id], nrows = tile_rows[tile_id];
-  const int h = blockIdx.y, kvh = h / (hq / hkv);
+  const int h = blockIdx.x, kvh = h / (hq / hkv);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int slot = slot_of_token[row0];
   const int pos0 = positions[row0];
@@ -340,10 +343,10 @@ attention_prefill_tc_single_kernel(const __grid_constant__ CUtensorMap map_q, co
   const int first_key = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
   const int item_lo = first_key / ATC_KEYS, tile_hi = pos_last / ATC_KEYS;
   const int item_tiles = (slot >= 0 && nrows > 0) ? tile_hi - item_lo + 1 : 0;
-  // the item's key tiles in gridDim.z runs of equal length; blocks past the last run have nothing to do
-  const int chunk = (item_tiles + (int)gridDim.z - 1) / (int)gridDim.z;
+  // the item's key tiles in `num_runs` runs of equal length; blocks past the last run have nothing to do
+  const int chunk = (item_tiles + nruns - 1) / nruns;
   const int nsplit = chunk > 0 ? (item_tiles + chunk - 1) / chunk : 1;
-  const int split = blockIdx.z;
+  const int split = blockIdx.y % nruns;
   const bool active = split < nsplit;
   const int tile_lo = item_lo + split * chunk;
   const int ntiles = (active && chunk > 0) ? min(chunk, item_tiles - split * chunk) : 0;
@@ -554,7 +557,7 @@ attention_prefill_tc_single_kernel(const __grid_constant__ CUtensorMap map_q, co
     if (!sh->group_bad && active) {
       const size_t item = (size_t)tile_id * hq + h;
       atc_finish<HD>(tmem_o + lane_addr, ntiles > 0, m, l, row, nrows, out + ((size_t)(row0 + row) * hq + h) * HD, nsplit, split,
-                     scratch + item * gridDim.z * ATC_SPLIT_WORDS(HD), counters + item, 1, &sh->last_flag);
+                     scratch + item * nruns * ATC_SPLIT_WORDS(HD), counters + item, 1, &sh->last_flag);
       atc_fence_before();
     }
   }
@@ -588,7 +591,7 @@ attention_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, cons
                             const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
                             const int* __restrict__ positions, const int* __restrict__ slot_of_token,
                             const int* __restrict__ block_table, int max_pages, int num_pages, int hq, int hkv,
-                            int page_size, int window, float scale_log2, float* __restrict__ scratch,
+                            int page_size, int window, float scale_log2, int num_runs, float* __restrict__ scratch,
                             int* __restrict__ counters) {
   constexpr int PANELS = HD / 64;          // 64-column panels of Q, K and V
   constexpr int PANEL_BYTES = 128 * 128;   // 128 rows of 128 bytes
@@ -601,10 +604,13 @@ attention_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, cons
   unsigned char* k_s = v_s + 2 * KV_BYTES;   // two stages
   volatile int* abort_flag = &sh->abort_flag;
 
-  const int tile_id = gridDim.x - 1 - blockIdx.x;  // the longest tiles first
+  // blocks are handed out in the order of blockIdx.x, then .y: the head pairs of the last tile's first run of keys,
+  // those of its second run, ..., then the tile before it: the longest rows of key tiles first, their runs together
+  const int nruns = num_runs;
+  const int tile_id = (int)(gridDim.y / nruns) - 1 - (int)(blockIdx.y / nruns);
   const int row0 = tile_row0[tile_id], nrows = tile_rows[tile_id];
   const int groups = hq / hkv, pairs = (groups + 1) >> 1;
-  const int kvh = blockIdx.y / pairs, pair = blockIdx.y - kvh * pairs;
+  const int kvh = blockIdx.x / pairs, pair = blockIdx.x - kvh * pairs;
   const int head_a = kvh * groups + 2 * pair;
   const bool has_b = 2 * pair + 1 < groups;  // a group of an odd number of heads leaves its last head alone
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -614,10 +620,10 @@ attention_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const int first_key = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
   const int item_lo = first_key / ATC_KEYS, tile_hi = pos_last / ATC_KEYS;
   const int item_tiles = (slot >= 0 && nrows > 0) ? tile_hi - item_lo + 1 : 0;
-  // the item's key tiles in gridDim.z runs of equal length; blocks past the last run have nothing to do
-  const int chunk = (item_tiles + (int)gridDim.z - 1) / (int)gridDim.z;
+  // the item's key tiles in `num_runs` runs of equal length; blocks past the last run have nothing to do
+  const int chunk = (item_tiles + nruns - 1) / nruns;
   const int nsplit = chunk > 0 ? (item_tiles + chunk - 1) / chunk : 1;
-  const int split = blockIdx.z;
+  const int split = blockIdx.y % nruns;
   const bool active = split < nsplit;
   const int tile_lo = item_lo + split * chunk;
   const int ntiles = (active && chunk > 0) ? min(chunk, item_tiles - split * chunk) : 0;
@@ -847,7 +853,7 @@ attention_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, cons
     if (!sh->group_bad[x] && (x == 0 || has_b) && active) {
       const size_t item = (size_t)tile_id * hq + head_a + x;
       atc_finish<HD>(tmem_o + lane_addr, steps > 0, m, l, row, nrows, out + ((size_t)(row0 + row) * hq + head_a + x) * HD, nsplit,
-                     split, scratch + item * gridDim.z * ATC_SPLIT_WORDS(HD), counters + item, 1 + x, &sh->last_flag[x]);
+                     split, scratch + item * nruns * ATC_SPLIT_WORDS(HD), counters + item, 1 + x, &sh->last_flag[x]);
       atc_fence_before();
     }
   }
@@ -898,10 +904,11 @@ static int atc_launch_single(const CUtensorMap& mq, const CUtensorMap& mk, const
     MS_REQUIRE(e == cudaSuccess, "attention_prefill_tc: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  dim3 grid(num_tiles, hq, splits);
+  MS_REQUIRE((long long)num_tiles * splits <= 65535, "attention_prefill_tc: %d tiles in %d runs are more than one launch takes", num_tiles, splits);
+  dim3 grid(hq, num_tiles * splits);
   kern<<<grid, ATC_THREADS, smem, stream>>>(mq, mk, mv, (__nv_bfloat16*)out, tile_row0, tile_rows, positions, slot_of_token,
                                             block_table, max_pages, num_pages, hq, hkv, page_size, window, scale * ATC_LOG2E,
-                                            scratch, counters);
+                                            splits, scratch, counters);
   MS_LAUNCH_CHECK("attention_prefill_tc");
   return 0;
 }
@@ -923,10 +930,11 @@ static int atc_launch_pair(const CUtensorMap& mq, const CUtensorMap& mk, const C
     configured = true;
   }
   const int groups = hq / hkv;
-  dim3 grid(num_tiles, hkv * ((groups + 1) / 2), splits);  // a block attends a tile of rows with two heads of one group
+  MS_REQUIRE((long long)num_tiles * splits <= 65535, "attention_prefill_tc: %d tiles in %d runs are more than one launch takes", num_tiles, splits);
+  dim3 grid(hkv * ((groups + 1) / 2), num_tiles * splits);  // a block attends a tile of rows with two heads of one group
   kern<<<grid, ATC_PAIR_THREADS, smem, stream>>>(mq, mk, mv, (__nv_bfloat16*)out, tile_row0, tile_rows, positions, slot_of_token,
                                                  block_table, max_pages, num_pages, hq, hkv, page_size, window, scale * ATC_LOG2E,
-                                                 scratch, counters);
+                                                 splits, scratch, counters);
   MS_LAUNCH_CHECK("attention_prefill_tc");
   return 0;
 }
@@ -998,7 +1006,7 @@ MS_API int ms_attention_prefill_tc(const void* q, const void* k_pages, const voi
                                    int hkv, int hd, int page_size, int window, float scale, int splits, float* scratch,
                                    long long scratch_words, int* counters, long long num_counters, cudaStream_t stream) {
   if (num_tiles == 0) return 0;
-  MS_REQUIRE(num_tiles > 0 && total_rows > 0 && hq > 0 && hkv > 0 && hq % hkv == 0 && hq <= 65535, "attention_prefill_tc: bad sizes");
+  MS_REQUIRE(num_tiles > 0 && total_rows > 0 && hq > 0 && hkv > 0 && hq % hkv == 0, "attention_prefill_tc: bad sizes");
   MS_REQUIRE(ms_attention_prefill_tc_supports(hd, page_size),
              "attention_prefill_tc: head_dim %d (64 or 128) or page size %d (a power of two from 8) is not covered", hd, page_size);
   MS_REQUIRE(((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)out) % 16 == 0, "attention_prefill_tc: operands must be 16-byte aligned");

@@ -475,10 +475,13 @@ class ModelRunner:
         ops.count_launches(launches)
         return logits[: len(entries)]
 
-    def step(self, entries: Sequence[StepEntry], reserved: bool = False, sampled: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], reserved: bool = False, sampled: Optional[torch.Tensor] = None,
+             tap=None) -> torch.Tensor:
         """Runs the entries as one batch.  Returns float32 logits [wanted, vocab] on the device, in the
         order of the entries and of their `want` lists (a view of scratch memory: valid until the next step).
-        `sampled`: the int32 device tensor that entries with `from_sampled` take their token from."""
+        `sampled`: the int32 device tensor that entries with `from_sampled` take their token from.
+        `tap(i, hidden)`: called after the embedding (i = -1) and after every run of a layer with the float32 hidden
+        rows [rows of the step, hidden]; such a step is run plainly, never from a captured graph."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         self._sampled = sampled
         self._check(entries)
@@ -490,9 +493,11 @@ class ModelRunner:
             idx = torch.tensor(fresh, dtype=torch.int64, device=self.device)
             for st in self.states.values():
                 st.index_fill_(0, idx, 0.0)
-        shape = self._graph_shape(entries)
+        shape = self._graph_shape(entries) if tap is None else None
         if shape is not None:
             logits = self._decode_with_graph(entries, *shape)
+        elif tap is not None:
+            logits = self.model.forward(self._stage(entries), self.bindings, tap)
         else:
             logits = self._step_general(entries)
         for e in entries:

@@ -88,21 +88,30 @@ class DecoderModel:
 
     # -- one step ---------------------------------------------------------------
 
-    def forward(self, ctx, caches: Sequence) -> torch.Tensor:
+    def forward(self, ctx, caches: Sequence, tap=None) -> torch.Tensor:
         """Runs the T token rows of `ctx` through the run order and returns float32 logits
         [num_wanted, vocab] for `ctx.want_rows`.  `caches[i]` is the cache binding of run i
-        (its own, or the one it reads)."""
+        (its own, or the one it reads).  `tap(i, hidden)`, if given, is called after every run with a
+        copy of the float32 hidden rows [T, hidden] as they stand after it (and with i = -1 after the
+        embedding): what the reference's `set_layer_dump` writes to files
+        (crates/mach-model/src/batched.rs:3051-3088 of gqf2008/machserve), for finding the first layer at which two
+        implementations part."""
         rt, spec = self.rt, self.spec
         ws = rt.workspace
         t = ctx.token_ids.shape[0]
         residual = ws.get("model.residual", (t, spec.hidden_size), torch.float32)
         self.embedding.forward(ctx, residual)
+        if tap is not None:
+            tap(-1, residual.clone())
         pending = None
         for i, run in enumerate(spec.run_order):
             block = self.blocks[run.layer]
             if not block.accepts_row_stats:
                 pending = as_delta(pending)  # a block of another kind sees a delta or None, as every norm does
             pending = block.forward(ctx, residual, pending, caches[i], run.cache_of is None)
+            if tap is not None:  # the delta a block hands on is part of the hidden rows after it
+                delta = as_delta(pending)
+                tap(i, residual.clone() if delta is None else residual + delta[: residual.shape[0]].float())
         w = ctx.want_rows.shape[0]
         final = ws.get("model.final", (w, spec.hidden_size), rt.dtype)
         self.final_norm.forward(residual, as_delta(pending), final, rows=ctx.want_rows)

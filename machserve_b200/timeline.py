@@ -10,8 +10,9 @@ buffer, runs steps and turns the records into a table:
     python -m machserve_b200.timeline --shape qwen2.5-0.5b --batch 8 --context 2048 [--layers 4]
     python -m machserve_b200.timeline --model DIR --batch 4 --context 300
 
-The reference's counterpart is its per-phase event timing behind MACH_STEP_PROFILE
-(crates/mach-server/src/main.rs:7-37 of gqf2008/machserve), which brackets phases with events on the host.
+The reference has two counterparts: per-layer event triples behind MACH_STEP_PROFILE
+(crates/mach-model/src/batched.rs:197-266 of gqf2008/machserve) and clock stamps inside its small-row kernels behind
+a nullable pointer (crates/mach-model/src/kernels.rs:2671-2694); this is the second kind.
 
 Only kernels that carry the hooks appear (the small-row products and the decoding attention: the kernels of a
 decoding step of up to 16 rows).  The plain build has no hooks and pays nothing for them.

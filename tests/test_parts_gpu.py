@@ -388,3 +388,32 @@ def test_toy_parts_are_registered_built_and_stepped(tmp_path):
         MIXERS.unregister("toy_decay")
         FEED_FORWARDS.unregister("toy_routed")
         POSITION_ENCODINGS.unregister("toy_scale")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layer_dump_follows_the_plain_layers(model_root, dtype):
+    """The step function's tap gives the hidden rows after the embedding and after every layer: a prompt, then a
+    decoding step (in bfloat16 the few-row path, whose deltas are added by the products themselves)."""
+    from machserve_b200.engine import StepEntry
+    from tests.plain import embedding
+
+    d = make_model_dir(model_root, "B")
+    bf16 = dtype == "bfloat16"
+    cfg, w = read_model_dir(d, round_to_bf16=bf16)
+    runner = _runner(d, dtype, page=TINY["B"]["page"])
+    toks = random_tokens(cfg["vocab_size"], 12, 9)
+    want, x = [], embedding(w["model.embed_tokens.weight"], toks)
+    want.append(x)
+    for layer in range(cfg["num_hidden_layers"]):
+        x = decoder_layer(x, w, layer, cfg, np.arange(len(toks)))
+        want.append(x)
+    tol = BF16_TOL if bf16 else F32_TOL
+    got = {}
+    runner.step([StepEntry("a", toks[:11], [])], tap=lambda i, h: got.__setitem__(i, _n(h)))
+    assert sorted(got) == list(range(-1, cfg["num_hidden_layers"]))
+    for i in got:
+        assert_close(got[i], want[i + 1][:11], tol, f"hidden rows after run {i} of the prompt")
+    got.clear()
+    runner.step([StepEntry("a", toks[11:], [0])], tap=lambda i, h: got.__setitem__(i, _n(h)))
+    for i in got:
+        assert_close(got[i], want[i + 1][11:], tol, f"hidden rows after run {i} of the decoded token")
