@@ -434,32 +434,48 @@ template <int HD, bool FUSED>
 static int launch_decode_cluster(const void* q, DclRaw raw, const void* k_pages, const void* v_pages, void* out, const int* rows,
                                  const int* positions, const int* slot_of_token, const int* block_table,
                                  int max_pages, int num_pages, int tokens, int hq, int hkv, int page_size, int window,
-                                 float scale, int num_splits, int stages, int warps, cudaStream_t stream) {
+                                 float scale, int num_splits, int stages, int warps, int kpw, cudaStream_t stream) {
 #define MS_DCL_LAUNCH(KPW, WARPS)                                                                                        \
   return launch_decode_cluster_k<HD, FUSED, KPW, WARPS>(q, raw, k_pages, v_pages, out, rows, positions, slot_of_token,   \
                                                         block_table, max_pages, num_pages, tokens, hq, hkv, page_size,   \
                                                         window, scale, num_splits, stages, stream)
-  if (stages <= 4 && warps == 4) MS_DCL_LAUNCH(32, 4);  // few tiles a round: half a tile per warp keeps all four busy
+  // few tiles a round, or wide heads (a long chain of steps per key): smaller parts keep every warp busy
+  if (kpw == 0) kpw = warps == 8 ? 32 : HD > 64 ? 16 : stages <= 4 ? 32 : 64;
   if (warps == 8) MS_DCL_LAUNCH(32, 8);
+  if (kpw == 16) MS_DCL_LAUNCH(16, 4);
+  if (kpw == 32) MS_DCL_LAUNCH(32, 4);
   MS_DCL_LAUNCH(64, 4);
 #undef MS_DCL_LAUNCH
 }
 
 MS_TIMELINE_SETTER(ms_timeline_set_attention_decode_cluster)
 
-// The most tiles a block can hold at once for a head size (about 100 KB of shared memory).
+// The most tiles a block can hold at once for a head size: about 100 KB of shared memory, which leaves room on the
+// SM for the blocks of the kernels that follow (they request their weights early); 144 KB for wide heads, so that
+// a block still holds four tiles.
 MS_API int ms_attention_decode_cluster_max_stages(int hd) {
-  int s = (int)((100 * 1024) / ((size_t)2 * DCL_TILE * (hd + 8) * sizeof(__nv_bfloat16)));
+  const size_t room = hd > 64 ? 144 * 1024 : 100 * 1024;
+  int s = (int)(room / ((size_t)2 * DCL_TILE * (hd + 8) * sizeof(__nv_bfloat16)));
   return s < 1 ? 1 : (s > 8 ? 8 : s);
+}
+
+// How many blocks with `stages` tiles an SM holds at once (by shared memory and by threads).
+MS_API int ms_attention_decode_cluster_blocks_per_sm(int hd, int stages, int warps) {
+  const size_t per_block = dcl_smem_bytes(hd, stages, warps) + 1024 + 16 * (size_t)hd * 4 + 1200;  // + the system's share and the static arrays
+  int n = (int)((size_t)233472 / per_block);
+  const int by_threads = 2048 / (warps * 32);
+  n = n > by_threads ? by_threads : n;
+  return n > 32 ? 32 : n;
 }
 
 static int decode_cluster_dispatch(const void* q, const DclRaw* raw, void* k_pages, void* v_pages, void* out,
                                    const int* rows, const int* positions, const int* slot_of_token,
                                    const int* block_table, int max_pages, int num_pages, int tokens, int hq, int hkv,
                                    int hd, int page_size, int window, float scale, int num_splits, int stages,
-                                   int warps, cudaStream_t stream) {
+                                   int warps, int kpw, cudaStream_t stream) {
   if (tokens == 0) return 0;
   MS_REQUIRE(warps == 4 || warps == 8, "attention_decode_cluster: 4 or 8 warps a block, not %d", warps);
+  MS_REQUIRE(kpw == 0 || kpw == 16 || kpw == 32 || kpw == 64, "attention_decode_cluster: a warp takes 16, 32 or 64 keys at a time (0: by rule), not %d", kpw);
   MS_REQUIRE(tokens > 0 && hq > 0 && hkv > 0 && hq % hkv == 0 && hkv <= 65535, "attention_decode_cluster: bad head counts hq=%d hkv=%d", hq, hkv);
   MS_REQUIRE(hd % 16 == 0 && hd >= 16 && hd <= 128 && hq / hkv <= 16,
              "attention_decode_cluster: head_dim %d (multiples of 16 up to 128) or group size %d (up to 16) is not covered", hd, hq / hkv);
@@ -473,10 +489,10 @@ static int decode_cluster_dispatch(const void* q, const DclRaw* raw, void* k_pag
   case N:                                                                                                               \
     return raw ? launch_decode_cluster<N, true>(nullptr, *raw, k_pages, v_pages, out, rows, positions, slot_of_token,   \
                                                 block_table, max_pages, num_pages, tokens, hq, hkv, page_size, window,  \
-                                                scale, num_splits, stages, warps, stream)                               \
+                                                scale, num_splits, stages, warps, kpw, stream)                          \
                : launch_decode_cluster<N, false>(q, none, k_pages, v_pages, out, rows, positions, slot_of_token,        \
                                                  block_table, max_pages, num_pages, tokens, hq, hkv, page_size, window, \
-                                                 scale, num_splits, stages, warps, stream)
+                                                 scale, num_splits, stages, warps, kpw, stream)
   switch (hd) {
     MS_DCL_CASE(16);
     MS_DCL_CASE(32);
@@ -494,15 +510,16 @@ static int decode_cluster_dispatch(const void* q, const DclRaw* raw, void* k_pag
 
 // As ms_attention_decode, without scratch memory.  num_splits: 1, 2, 4 or 8 (the cluster size).
 // stages: tiles of 64 keys a block holds at once, 1 .. ms_attention_decode_cluster_max_stages(hd).
-// warps: 4, or 8 (half a tile per warp: for the few blocks of a small batch; with up to two stages 4 are used).
+// warps: 4, or 8 (half a tile per warp: for the few blocks of a small batch).  keys_per_warp: the part of a tile a
+// warp takes at a time with four warps, 16, 32 or 64; 0 chooses by the number of stages.
 MS_API int ms_attention_decode_cluster(const void* q, const void* k_pages, const void* v_pages, void* out,
                                        const int* rows, const int* positions, const int* slot_of_token,
                                        const int* block_table, int max_pages, int num_pages, int tokens, int hq, int hkv,
                                        int hd, int page_size, int window, float scale, int num_splits, int stages,
-                                       int warps, cudaStream_t stream) {
+                                       int warps, int keys_per_warp, cudaStream_t stream) {
   return decode_cluster_dispatch(q, nullptr, const_cast<void*>(k_pages), const_cast<void*>(v_pages), out, rows, positions,
                                  slot_of_token, block_table, max_pages, num_pages, tokens, hq, hkv, hd, page_size, window,
-                                 scale, num_splits, stages, warps, stream);
+                                 scale, num_splits, stages, warps, keys_per_warp, stream);
 }
 
 // The fused form: reads rows of q|k|v as the projection left them (bfloat16, row stride ld, a multiple of 8),
@@ -515,7 +532,7 @@ MS_API int ms_attention_decode_cluster_rope(const void* qkv, int ld, const float
                                             const int* positions, const int* slot_of_token, const int* block_table,
                                             int max_pages, int num_pages, int tokens, int hq, int hkv, int hd,
                                             int page_size, int window, float scale, int num_splits, int stages,
-                                            int warps, cudaStream_t stream) {
+                                            int warps, int keys_per_warp, cudaStream_t stream) {
   MS_REQUIRE(qkv != nullptr && cos_sin != nullptr, "attention_decode_cluster_rope: no rows or no rotary table");
   MS_REQUIRE(ld % 8 == 0 && ld >= (hq + (store ? 2 * hkv : 0)) * hd, "attention_decode_cluster_rope: row stride %d (a multiple of 8, at least %d)",
              ld, (hq + (store ? 2 * hkv : 0)) * hd);
@@ -524,5 +541,5 @@ MS_API int ms_attention_decode_cluster_rope(const void* qkv, int ld, const float
   const DclRaw raw = {(const __nv_bfloat16*)qkv, ld, bias, (const float2*)cos_sin, store ? 1 : 0};
   return decode_cluster_dispatch(nullptr, &raw, k_pages, v_pages, out, rows, positions, slot_of_token, block_table,
                                  max_pages, num_pages, tokens, hq, hkv, hd, page_size, window, scale, num_splits, stages,
-                                 warps, stream);
+                                 warps, keys_per_warp, stream);
 }

@@ -275,23 +275,27 @@ __device__ __forceinline__ void atc_finish(unsigned tmem_o_lane, bool have_o, fl
   }
   const float inv = sum > 0.f ? 1.f / sum : 0.f;
   if (row < nrows) {
+    // 32 columns at a time: all splits' values of them are requested together (a round trip to the L2 per chunk)
 #pragma unroll 1
-    for (int c = 0; c < HD; c += 8) {
-      float o[8];
+    for (int c = 0; c < HD; c += 32) {
+      float o[32];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) o[e] = 0.f;
+      for (int e = 0; e < 32; ++e) o[e] = 0.f;
 #pragma unroll
       for (int s = 0; s < ATC_MAX_SPLITS; ++s)
         if (s < nsplit) {
 #pragma unroll
-          for (int e = 0; e < 8; ++e)
+          for (int e = 0; e < 32; ++e)
             o[e] += w[s] * __ldcg(item_scratch + (size_t)s * ATC_SPLIT_WORDS(HD) + (size_t)(c + e) * ATC_ROWS + row);
         }
-      uint4 u;
-      __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&u);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) hh[e] = __floats2bfloat162_rn(o[2 * e] * inv, o[2 * e + 1] * inv);
-      *reinterpret_cast<uint4*>(dst + c) = u;
+      for (int j = 0; j < 4; ++j) {
+        uint4 u;
+        __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) hh[e] = __floats2bfloat162_rn(o[j * 8 + 2 * e] * inv, o[j * 8 + 2 * e + 1] * inv);
+        *reinterpret_cast<uint4*>(dst + c + j * 8) = u;
+      }
     }
   }
   if (row == 0) *counter = 0;
@@ -591,7 +595,7 @@ attention_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, cons
                             const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
                             const int* __restrict__ positions, const int* __restrict__ slot_of_token,
                             const int* __restrict__ block_table, int max_pages, int num_pages, int hq, int hkv,
-                            int page_size, int window, float scale_log2, int num_runs, float* __restrict__ scratch,
+                            int page_size, int window, float scale_log2, int num_runs, int alone, float* __restrict__ scratch,
                             int* __restrict__ counters) {
   constexpr int PANELS = HD / 64;          // 64-column panels of Q, K and V
   constexpr int PANEL_BYTES = 128 * 128;   // 128 rows of 128 bytes
@@ -609,10 +613,11 @@ attention_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const int nruns = num_runs;
   const int tile_id = (int)(gridDim.y / nruns) - 1 - (int)(blockIdx.y / nruns);
   const int row0 = tile_row0[tile_id], nrows = tile_rows[tile_id];
-  const int groups = hq / hkv, pairs = (groups + 1) >> 1;
+  // `alone`: every block takes one head (launches of few blocks: twice as many of half the length)
+  const int groups = hq / hkv, pairs = alone ? groups : (groups + 1) >> 1;
   const int kvh = blockIdx.x / pairs, pair = blockIdx.x - kvh * pairs;
-  const int head_a = kvh * groups + 2 * pair;
-  const bool has_b = 2 * pair + 1 < groups;  // a group of an odd number of heads leaves its last head alone
+  const int head_a = kvh * groups + (alone ? pair : 2 * pair);
+  const bool has_b = !alone && 2 * pair + 1 < groups;  // a group of an odd number of heads leaves its last head alone
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int slot = slot_of_token[row0];
   const int pos0 = positions[row0];
@@ -917,7 +922,7 @@ template <int HD>
 static int atc_launch_pair(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, const int* tile_row0,
                            const int* tile_rows, int num_tiles, const int* positions, const int* slot_of_token,
                            const int* block_table, int max_pages, int num_pages, int hq, int hkv, int page_size, int window,
-                           float scale, int splits, float* scratch, int* counters, cudaStream_t stream) {
+                           float scale, int splits, int alone, float* scratch, int* counters, cudaStream_t stream) {
   // two heads' Q, two stages of K and of V (194 KB at head size 128); never less than half an SM's shared memory, so
   // that a block has the SM and all of its tensor memory to itself
   size_t smem = 1024 + 1024 + (size_t)(HD / 64) * 16384 * 6;
@@ -931,10 +936,11 @@ static int atc_launch_pair(const CUtensorMap& mq, const CUtensorMap& mk, const C
   }
   const int groups = hq / hkv;
   MS_REQUIRE((long long)num_tiles * splits <= 65535, "attention_prefill_tc: %d tiles in %d runs are more than one launch takes", num_tiles, splits);
-  dim3 grid(hkv * ((groups + 1) / 2), num_tiles * splits);  // a block attends a tile of rows with two heads of one group
+  // a block attends a tile of rows with two heads of one group, or with one head
+  dim3 grid(hkv * (alone ? groups : (groups + 1) / 2), num_tiles * splits);
   kern<<<grid, ATC_PAIR_THREADS, smem, stream>>>(mq, mk, mv, (__nv_bfloat16*)out, tile_row0, tile_rows, positions, slot_of_token,
                                                  block_table, max_pages, num_pages, hq, hkv, page_size, window, scale * ATC_LOG2E,
-                                                 splits, scratch, counters);
+                                                 splits, alone, scratch, counters);
   MS_LAUNCH_CHECK("attention_prefill_tc");
   return 0;
 }
@@ -982,29 +988,65 @@ MS_API long long ms_attention_prefill_tc_scratch_words(int num_tiles, int hq, in
   return (long long)num_tiles * hq * splits * ATC_SPLIT_WORDS(hd);
 }
 
-// How many runs the key tiles of every item are cut into so that a launch fills the GPU: few tiles of rows (a short
-// prompt, a portion of a long one) would leave most SMs idle behind the blocks with the longest rows of key tiles.
-// `max_keys`: the most keys any row of the launch sees.
-MS_API int ms_attention_prefill_tc_splits(int num_tiles, int hq, int hkv, int hd, int max_keys, int sm_count) {
-  if (num_tiles <= 0 || hq <= 0 || hkv <= 0) return 1;
+// How a launch is laid out so that it fills the GPU: few tiles of rows (a short prompt, a portion of a long one) would
+// leave most SMs idle behind the blocks with the longest rows of key tiles.  plan[0]: the number of runs the key tiles
+// of every item are cut into for different blocks (1 to 4).  plan[1]: 1 if, at head size 128, every block should take
+// one head instead of two of a group.  `max_keys`: the most keys any row of the launch sees; `total_key_tiles`: the
+// tiles of 128 keys that the launch's tiles of rows see, in all (0: every tile sees max_keys).
+//
+// Head size 64 (two blocks per SM): as many runs as fill the places, at least four key tiles a run.
+// Head size 128: the cheapest of the eight layouts by a model of the launch's time, fitted to measurements on B200
+// (1.5B and 7B head counts, 128 to 2,048 rows, 128 to 4,096 keys; us): a block costs 13 at its start and end and 2.6
+// per key tile with two heads, 9.5 and 2.3 with one; a launch takes as long as its longest block or as its work
+// spread over the SMs, whichever is more (blocks of equal length: as the waves they come in); runs of key tiles cost
+// 4 + their number for the merge.
+MS_API void ms_attention_prefill_tc_plan(int num_tiles, int hq, int hkv, int hd, int max_keys, int total_key_tiles,
+                                         int sm_count, int* plan) {
+  plan[0] = 1;
+  plan[1] = 0;
+  if (num_tiles <= 0 || hq <= 0 || hkv <= 0 || sm_count <= 0) return;
   const int groups = hq / hkv;
-  const long long blocks = (long long)num_tiles * (hd == 64 ? hq : hkv * ((groups + 1) / 2));
-  const long long slots = (long long)sm_count * (hd == 64 ? 2 : 1);
-  int splits = (int)(slots / (blocks > 0 ? blocks : 1));
   const int key_tiles = (max_keys + ATC_KEYS - 1) / ATC_KEYS;
-  if (splits > key_tiles / 4) splits = key_tiles / 4;  // at least four key tiles per run: a merge costs about one
-  if (splits > ATC_MAX_SPLITS) splits = ATC_MAX_SPLITS;
-  return splits < 1 ? 1 : splits;
+  if (hd == 64) {
+    const long long blocks = (long long)num_tiles * hq;
+    int splits = (int)(2LL * sm_count / blocks);
+    if (splits > key_tiles / 4) splits = key_tiles / 4;
+    if (splits > ATC_MAX_SPLITS) splits = ATC_MAX_SPLITS;
+    plan[0] = splits < 1 ? 1 : splits;
+    return;
+  }
+  const float all_tiles = total_key_tiles > 0 ? (float)total_key_tiles : (float)num_tiles * key_tiles;
+  const float mean_tiles = all_tiles / (float)num_tiles;
+  const bool alike = mean_tiles >= 0.8f * key_tiles;  // a portion deep in its prompt: blocks of equal length come in waves
+  float best = 0.f;
+  for (int alone = 0; alone < 2; ++alone) {
+    const float fixed = alone ? 9.5f : 13.f, step = alone ? 2.3f : 2.6f;
+    const float heads = (float)(alone ? hq : hkv * ((groups + 1) / 2));
+    for (int s = 1; s <= ATC_MAX_SPLITS && (s == 1 || 2 * s <= key_tiles); ++s) {
+      const float blocks = heads * (float)num_tiles * s;
+      const float longest = fixed + (float)((key_tiles + s - 1) / s) * step;
+      const float spread = (blocks * fixed + heads * all_tiles * step) / (float)sm_count;
+      const float waves = (float)(((long long)blocks + sm_count - 1) / sm_count) * (fixed + mean_tiles / s * step);
+      const float body = alike ? (longest > waves ? longest : waves) : (longest > spread ? longest : spread);
+      const float t = s > 1 ? (body + 4.f + s) * 1.1f : body;  // (runs have to earn a tenth more than they promise)
+      if (best == 0.f || t < best - 0.05f) {
+        best = t;
+        plan[0] = s;
+        plan[1] = alone;
+      }
+    }
+  }
 }
 
 // As ms_attention_prefill, with tiles of up to 128 rows.  q, out: bfloat16 [total_rows, hq*hd].  `splits` (1 to 4): the
 // key tiles of every item go to that many blocks, which meet in `scratch` (ms_attention_prefill_tc_scratch_words) and
-// count themselves in `counters` (num_tiles * hq of them, all zero).
+// count themselves in `counters` (num_tiles * hq of them, all zero).  `alone` (head size 128): a block takes one head, not two.
 MS_API int ms_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, void* out, int total_rows,
                                    const int* tile_row0, const int* tile_rows, int num_tiles, const int* positions,
                                    const int* slot_of_token, const int* block_table, int max_pages, int num_pages, int hq,
-                                   int hkv, int hd, int page_size, int window, float scale, int splits, float* scratch,
-                                   long long scratch_words, int* counters, long long num_counters, cudaStream_t stream) {
+                                   int hkv, int hd, int page_size, int window, float scale, int splits, int alone,
+                                   float* scratch, long long scratch_words, int* counters, long long num_counters,
+                                   cudaStream_t stream) {
   if (num_tiles == 0) return 0;
   MS_REQUIRE(num_tiles > 0 && total_rows > 0 && hq > 0 && hkv > 0 && hq % hkv == 0, "attention_prefill_tc: bad sizes");
   MS_REQUIRE(ms_attention_prefill_tc_supports(hd, page_size),
@@ -1026,5 +1068,5 @@ MS_API int ms_attention_prefill_tc(const void* q, const void* k_pages, const voi
     return atc_launch_single(mq, mk, mv, out, tile_row0, tile_rows, num_tiles, positions, slot_of_token, block_table, max_pages,
                              num_pages, hq, hkv, page_size, window, scale, splits, scratch, counters, stream);
   return atc_launch_pair<128>(mq, mk, mv, out, tile_row0, tile_rows, num_tiles, positions, slot_of_token, block_table, max_pages,
-                              num_pages, hq, hkv, page_size, window, scale, splits, scratch, counters, stream);
+                              num_pages, hq, hkv, page_size, window, scale, splits, alone ? 1 : 0, scratch, counters, stream);
 }

@@ -73,9 +73,10 @@ class _Signatures:
     ms_attention_generic = [P, P, P, P, I, I, P, P, P, I, I, I, I, I, I, I, I, F, P]
     ms_gemm_f32 = [P, I, P, P, P, I, I, I, I, P]
     ms_attention_decode = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P]
-    ms_attention_decode_cluster = [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, I, P]
-    ms_attention_decode_cluster_rope = [P, I, P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, I, P]
-    ms_attention_prefill_tc = [P, P, P, P, I, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, LL, P, LL, P]
+    ms_attention_decode_cluster = [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, I, I, P]
+    ms_attention_decode_cluster_rope = [P, I, P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, I, I, P]
+    ms_attention_prefill_tc = [P, P, P, P, I, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, LL, P, LL, P]
+    ms_attention_prefill_tc_plan = [I, I, I, I, I, I, I, P]
     ms_attention_prefill = [P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P]
     ms_gemm_small_m = [P, I, P, P, I, I, I, I, I, I, P]
     ms_gemm_small_m_silu_mul = [P, I, P, P, P, I, I, I, I, I, P]
@@ -352,8 +353,13 @@ def attention_decode_cluster_max_stages(head_dim: int) -> int:
     return int(lib().ms_attention_decode_cluster_max_stages(int(head_dim)))
 
 
+def attention_decode_cluster_blocks_per_sm(head_dim: int, stages: int, warps: int = 4) -> int:
+    """How many blocks of the kernel with `stages` tiles each an SM holds at once."""
+    return int(lib().ms_attention_decode_cluster_blocks_per_sm(int(head_dim), int(stages), int(warps)))
+
+
 def attention_decode_cluster(q, k_pages, v_pages, out, positions, slot_of_token, block_table, num_heads, num_kv_heads,
-                             head_dim, window, scale, num_splits, stages, rows=None, num_rows=None, warps=4):
+                             head_dim, window, scale, num_splits, stages, rows=None, num_rows=None, warps=4, keys_per_warp=0):
     """As attention_decode, with the splits of a row held by one thread-block cluster (1, 2, 4 or 8) and merged in
     shared memory: no scratch.  Keys and values of earlier positions are requested before the kernel waits for its
     predecessor in the stream.  `stages`: tiles of 64 keys a block holds at once."""
@@ -369,7 +375,7 @@ def attention_decode_cluster(q, k_pages, v_pages, out, positions, slot_of_token,
         lib().ms_attention_decode_cluster(
             _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(rows), _ptr(positions), _ptr(slot_of_token),
             _ptr(block_table), block_table.shape[1], k_pages.shape[0], tokens, num_heads, num_kv_heads, head_dim,
-            k_pages.shape[2], int(window or 0), float(scale), int(num_splits), int(stages), int(warps), _stream(),
+            k_pages.shape[2], int(window or 0), float(scale), int(num_splits), int(stages), int(warps), int(keys_per_warp), _stream(),
         ),
         "attention_decode_cluster",
     )
@@ -378,7 +384,7 @@ def attention_decode_cluster(q, k_pages, v_pages, out, positions, slot_of_token,
 
 def attention_decode_cluster_rope(qkv, bias, cos_sin, store, k_pages, v_pages, out, positions, slot_of_token, block_table,
                                   num_heads, num_kv_heads, head_dim, window, scale, num_splits, stages, rows=None,
-                                  num_rows=None, warps=4):
+                                  num_rows=None, warps=4, keys_per_warp=0):
     """rope_kv_store and attention_decode_cluster in one kernel, for rows that are alone in their sequences: reads
     rows of q|k|v (k and v only if `store`) as the projection left them, adds the bias, rotates q and k (full rotary,
     pairs j and j + head_dim/2, table [positions, head_dim/2, 2]), writes k and v into the cache, and attends."""
@@ -401,7 +407,7 @@ def attention_decode_cluster_rope(qkv, bias, cos_sin, store, k_pages, v_pages, o
             _ptr(qkv), qkv.stride(0), _ptr(bias), _ptr(cos_sin), 1 if store else 0, _ptr(k_pages), _ptr(v_pages), _ptr(out),
             _ptr(rows), _ptr(positions), _ptr(slot_of_token), _ptr(block_table), block_table.shape[1], k_pages.shape[0],
             tokens, num_heads, num_kv_heads, head_dim, k_pages.shape[2], int(window or 0), float(scale), int(num_splits),
-            int(stages), int(warps), _stream(),
+            int(stages), int(warps), int(keys_per_warp), _stream(),
         ),
         "attention_decode_cluster_rope",
     )
@@ -668,10 +674,15 @@ def attention_prefill_tc_supports(head_dim: int, page_size: int) -> bool:
     return bool(lib().ms_attention_prefill_tc_supports(int(head_dim), int(page_size)))
 
 
-def attention_prefill_tc_splits(num_tiles: int, num_heads: int, num_kv_heads: int, head_dim: int, max_keys: int) -> int:
-    """Into how many runs the kernel should cut every item's key tiles so that the launch fills the GPU (1 to 4)."""
-    return int(lib().ms_attention_prefill_tc_splits(int(num_tiles), int(num_heads), int(num_kv_heads), int(head_dim),
-                                                    int(max_keys), sm_count()))
+def attention_prefill_tc_plan(num_tiles: int, num_heads: int, num_kv_heads: int, head_dim: int, max_keys: int,
+                              key_tiles: int = 0):
+    """(splits, alone): into how many runs the kernel should cut every item's key tiles so that the launch fills the
+    GPU (1 to 4), and whether, at head size 128, every block should take one head instead of two of a group.
+    `key_tiles`: the tiles of 128 keys that the launch's tiles of rows see, in all (0: every tile sees `max_keys`)."""
+    plan = (ctypes.c_int * 2)()
+    lib().ms_attention_prefill_tc_plan(int(num_tiles), int(num_heads), int(num_kv_heads), int(head_dim), int(max_keys),
+                                       int(key_tiles), sm_count(), plan)
+    return int(plan[0]), bool(plan[1])
 
 
 def attention_prefill_tc_scratch_words(num_tiles: int, num_heads: int, head_dim: int, splits: int) -> int:
@@ -683,13 +694,13 @@ def attention_prefill_tc_scratch_words(num_tiles: int, num_heads: int, head_dim:
 
 
 def attention_prefill_tc(q, k_pages, v_pages, out, tile_row0, tile_rows, num_tiles, positions, slot_of_token, block_table,
-                         num_heads, num_kv_heads, head_dim, window, scale, splits=1, scratch=None, counters=None):
+                         num_heads, num_kv_heads, head_dim, window, scale, splits=1, scratch=None, counters=None, alone=False):
     """Paged causal attention for tiles of up to 128 consecutive rows of one sequence on tcgen05 tensor cores
     (TMA-fed, scores in tensor memory and taken into registers a row per thread, probabilities back into tensor
     memory, outputs accumulated there over all key tiles).  Head sizes 64 (one head per block) and 128 (two heads of a
     group per block, which share the keys and values), page sizes 8, 16, 32, ...  With `splits` > 1 the key tiles of
     every (tile, head) go to that many blocks, which meet in `scratch` (float32) and count themselves in `counters`
-    (int32, num_tiles * num_heads of them, all zero before and after)."""
+    (int32, num_tiles * num_heads of them, all zero before and after).  `alone` (head size 128): one head per block."""
     _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16,
           "attention_prefill_tc: bfloat16 only")
     _need(q.is_contiguous() and out.is_contiguous() and k_pages.is_contiguous() and v_pages.is_contiguous(),
@@ -704,7 +715,7 @@ def attention_prefill_tc(q, k_pages, v_pages, out, tile_row0, tile_rows, num_til
         lib().ms_attention_prefill_tc(
             _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), q.shape[0], _ptr(tile_row0), _ptr(tile_rows), int(num_tiles),
             _ptr(positions), _ptr(slot_of_token), _ptr(block_table), block_table.shape[1], k_pages.shape[0], num_heads,
-            num_kv_heads, head_dim, k_pages.shape[2], int(window or 0), float(scale), int(splits), _ptr(scratch),
+            num_kv_heads, head_dim, k_pages.shape[2], int(window or 0), float(scale), int(splits), 1 if alone else 0, _ptr(scratch),
             scratch.numel() if scratch is not None else 0, _ptr(counters), counters.numel() if counters is not None else 0,
             _stream(),
         ),

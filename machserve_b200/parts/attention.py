@@ -94,6 +94,7 @@ class Attention(Mixer):
         self.fast = (rt.dtype == torch.bfloat16 and ops.attention_decode_supports(self.hd, self.hq // self.hkv)
                      and ops.attention_prefill_supports(self.hd))
         self.max_stages = ops.attention_decode_cluster_max_stages(self.hd) if self.fast else 0
+        self._launch_cache = {}
         # decoding steps: bias, rotation and cache write inside the attention kernel (full rotary with half pairing)
         self.fuse_encode = (self.fast and self.table is not None and self.position.rotary_dim == self.hd
                             and not self.position.interleaved and self.hd % 16 == 0)
@@ -113,6 +114,7 @@ class Attention(Mixer):
         portions of prompts are cut into tiles of up to 64 and up to 128 consecutive rows for the two prompt kernels."""
         single, t0, tn, b0, bn = [], [], [], [], []
         longest = longest_portion = 0  # the most keys a decoding row sees, and a row of a portion
+        key_tiles = 0                  # tiles of 128 keys that the tiles of 128 rows see, in all
         for row, n, start in zip(step.row0, step.count, step.start):
             if n == 1:
                 single.append(row)
@@ -123,10 +125,17 @@ class Attention(Mixer):
                     t0.append(row + a)
                     tn.append(min(self.TILE, n - a))
                 for a in range(0, n, self.BIG_TILE):
+                    rows = min(self.BIG_TILE, n - a)
                     b0.append(row + a)
-                    bn.append(min(self.BIG_TILE, n - a))
+                    bn.append(rows)
+                    first = max(0, start + a - self.window + 1) if self.window else 0
+                    key_tiles += (start + a + rows - 1) // self.BIG_TILE - first // self.BIG_TILE + 1
         lists = {"single_rows": single, "tile_row0": t0, "tile_rows": tn, "big_tile_row0": b0, "big_tile_rows": bn}
-        return WorkPlan(lists, (-(-longest // self.CONTEXT_BUCKET), -(-longest_portion // self.CONTEXT_BUCKET)))
+        # what the launches depend on beside the lengths of the lists, in coarse steps (a step is replayed from a graph
+        # under these): the longest context of a decoding row, of a portion's row, and the mean number of key tiles
+        # that a tile of a portion's rows sees
+        mean_key_tiles = -(-key_tiles // (2 * len(b0))) * 2 if b0 else 0
+        return WorkPlan(lists, (-(-longest // self.CONTEXT_BUCKET), -(-longest_portion // self.CONTEXT_BUCKET), mean_key_tiles))
 
     # -- with few rows in bfloat16: the norm in front and the add behind inside the products -------------------------
     fused_rows = 16
@@ -205,6 +214,37 @@ class Attention(Mixer):
             return self._attend_single(ctx, None, cache, out, raw=(qkv, store))
         return self.attend(ctx, self.encode_store(ctx, qkv, cache, store), cache, out)
 
+    def _single_launch(self, units: int, tiles: int):
+        """(splits, stages, warps) for `units` (row, kv head) pairs whose longest run of keys has `tiles` tiles of 64.
+        What the measurements on B200 (head sizes 64 and 128, 8 to 64 rows, 1,000 to 2,048 keys) come to: all blocks
+        of the launch are resident at once (a second wave costs more than fewer, longer blocks), as many splits as
+        that allows up to three and a half blocks per SM, never more blocks than half the tiles.  A block holds its
+        whole run of tiles when that fits (all of it is requested before the wait for the preceding kernel), else it
+        goes through the run with four or two tiles at a time, or with one when the run is short."""
+        key = (units, tiles)
+        hit = self._launch_cache.get(key)
+        if hit is not None:
+            return hit
+        sm, hd = self.rt.sm_count, self.hd
+        choice = None
+        for splits in (8, 4, 2, 1):
+            if splits > 1 and (2 * splits > tiles or splits * units > 3.5 * sm):
+                continue
+            blocks, per = splits * units, -(-tiles // splits)
+            ring = [n for n in (4, 2, 1) if n < per and n <= self.max_stages and (n <= 2 or hd <= 64) and (n > 1 or per <= 4)]
+            for stages in ([per] if per <= self.max_stages else []) + ring:
+                if blocks <= sm * ops.attention_decode_cluster_blocks_per_sm(hd, stages):
+                    choice = (splits, stages)
+                    break
+            if choice:
+                break
+        splits, stages = choice or (1, min(2, self.max_stages, tiles))
+        blocks = splits * units
+        # the few blocks of a small batch (one per SM at most): eight warps, half a tile each
+        warps = 8 if stages >= 4 and blocks <= sm and hd <= 64 else 4
+        self._launch_cache[key] = (splits, stages, warps)
+        return splits, stages, warps
+
     def _attend_single(self, ctx, q, cache, out, raw=None):
         """Rows that are alone in their sequences: a cluster of blocks per (row, kv head)."""
         work = ctx.work[self.PLAN]
@@ -213,16 +253,7 @@ class Attention(Mixer):
         tiles = (work.shape[0] * self.CONTEXT_BUCKET + 63) // 64  # of the longest decoding context, by bucket
         if self.window:
             tiles = min(tiles, (self.window + 63) // 64 + 1)
-        # about two blocks for every SM, never more blocks than tiles
-        splits = 1
-        while splits < 8 and splits * t * self.hkv < 2 * rt.sm_count and 2 * splits <= tiles:
-            splits *= 2
-        # few blocks: each holds its whole run of tiles, requested before the wait for the preceding
-        # kernel; many blocks: two tiles each, so that more blocks fit on an SM (measured at batch 64)
-        many = splits * t * self.hkv >= 2 * rt.sm_count
-        stages = max(1, min(2 if many else self.max_stages, -(-tiles // splits)))
-        # the few blocks of a small batch (one per SM at most): eight warps, half a tile each
-        warps = 8 if stages >= 4 and splits * t * self.hkv <= rt.sm_count else 4
+        splits, stages, warps = self._single_launch(t * self.hkv, tiles)
         if raw is not None:
             qkv, store = raw
             return ops.attention_decode_cluster_rope(
@@ -258,7 +289,7 @@ class Attention(Mixer):
             max_keys = work.shape[1] * self.CONTEXT_BUCKET
             if self.window:
                 max_keys = min(max_keys, self.window + self.BIG_TILE)
-            splits = ops.attention_prefill_tc_splits(n_tiles, self.hq, self.hkv, self.hd, max_keys)
+            splits, alone = ops.attention_prefill_tc_plan(n_tiles, self.hq, self.hkv, self.hd, max_keys, work.shape[2] * n_tiles)
             scratch = counters = None
             if splits > 1:
                 words = ops.attention_prefill_tc_scratch_words(n_tiles, self.hq, self.hd, splits)
@@ -268,6 +299,7 @@ class Attention(Mixer):
             ops.attention_prefill_tc(
                 q, cache.k_pages, cache.v_pages, out, lists["big_tile_row0"], lists["big_tile_rows"], n_tiles,
                 ctx.positions, ctx.slot_of_token, table, self.hq, self.hkv, self.hd, self.window, self.scale, splits, scratch, counters,
+                alone=alone,
             )
         elif sizes["tile_row0"]:
             ops.attention_prefill(

@@ -310,10 +310,12 @@ def test_attention_decode(lens, hq, hkv, hd, page, window, splits):
 
 
 @pytest.mark.parametrize("lens,hq,hkv,hd,page,window", ATT_CASES)
-@pytest.mark.parametrize("splits,stages,warps", [(1, 1, 4), (2, 8, 4), (4, 2, 4), (8, 1, 4), (8, 8, 4), (1, 4, 8), (2, 8, 8), (8, 5, 8)])
-def test_attention_decode_cluster(lens, hq, hkv, hd, page, window, splits, stages, warps):
+@pytest.mark.parametrize("splits,stages,warps,kpw", [(1, 1, 4, 0), (2, 8, 4, 0), (4, 2, 4, 0), (8, 1, 4, 0), (8, 8, 4, 0), (1, 4, 8, 0), (2, 8, 8, 0),
+                                                     (8, 5, 8, 0), (2, 2, 4, 16), (4, 1, 4, 32), (1, 3, 4, 64), (8, 4, 4, 16)])
+def test_attention_decode_cluster(lens, hq, hkv, hd, page, window, splits, stages, warps, kpw):
     """The cluster variant: splits merged in shared memory, several tiles in flight, the current row copied late;
-    four warps with a tile (or, with two stages, half a tile) each, and eight warps with half a tile each."""
+    four warps with a tile, half or a quarter of a tile each (`kpw`; 0: the kernel's own rule), and eight warps with
+    half a tile each."""
     import torch
     from machserve_b200 import ops
     if not ops.attention_decode_supports(hd, hq // hkv):
@@ -328,13 +330,13 @@ def test_attention_decode_cluster(lens, hq, hkv, hd, page, window, splits, stage
     pos1 = torch.cat([pos, torch.zeros(1, dtype=torch.int32, device=dev())])
     slot1 = torch.cat([slot, torch.full((1,), -1, dtype=torch.int32, device=dev())])  # a padding row at the end
     ops.attention_decode_cluster(q16, case.k_pages, case.v_pages, out, pos1, slot1, case.table, hq, hkv, hd, window,
-                                 hd ** -0.5, splits, stages, warps=warps)
+                                 hd ** -0.5, splits, stages, warps=warps, keys_per_warp=kpw)
     assert np.abs(N(out[:-1]) - want).max() <= 2.0 ** -7 * max(1.0, np.abs(want).max())
     assert (N(out[-1]) == 7.0).all()  # nothing is written for the padding row
     pick = np.array(sorted(set(range(0, len(rows), 2)) | {len(rows) - 1}), dtype=np.int32)
     out2 = torch.full((len(rows) + 1, hq * hd), 7.0, dtype=torch.bfloat16, device=dev())
     ops.attention_decode_cluster(q16, case.k_pages, case.v_pages, out2, pos1, slot1, case.table, hq, hkv, hd, window,
-                                 hd ** -0.5, splits, stages, rows=T(pick), num_rows=len(pick), warps=warps)
+                                 hd ** -0.5, splits, stages, rows=T(pick), num_rows=len(pick), warps=warps, keys_per_warp=kpw)
     assert torch.equal(out2[T(pick).long()], out[T(pick).long()])
     assert (N(out2)[np.setdiff1d(np.arange(len(rows)), pick)] == 7.0).all()
 
@@ -435,15 +437,18 @@ TC_ATT_CASES = [
 ]
 
 
-@pytest.mark.parametrize("splits", [1, 2, 3, 4])
+@pytest.mark.parametrize("splits,alone", [(1, False), (2, False), (3, False), (4, False), (1, True), (3, True)])
 @pytest.mark.parametrize("lens,hq,hkv,hd,page,window", TC_ATT_CASES)
-def test_attention_prefill_tc(lens, hq, hkv, hd, page, window, splits):
+def test_attention_prefill_tc(lens, hq, hkv, hd, page, window, splits, alone):
     """The tcgen05 kernel for portions of prompts: tiles of up to 128 rows, pages of several sizes, windows; the key
-    tiles of every (tile, head) in one run or split over two to four blocks that merge through scratch memory.  Run
-    twice on the same scratch memory: a launch leaves its counters as it found them."""
+    tiles of every (tile, head) in one run or split over two to four blocks that merge through scratch memory; at
+    head size 128 two heads of a group per block, or one (`alone`).  Run twice on the same scratch memory: a launch
+    leaves its counters as it found them."""
     import torch
     from machserve_b200 import ops
     assert ops.attention_prefill_tc_supports(hd, page)
+    if alone and hd == 64:
+        pytest.skip("at head size 64 a block always takes one head")
     case = PagedCase(lens, hq, hkv, hd, page, window)
     rows, tile0, tilen = [], [], []
     for s, n in enumerate(lens):
@@ -465,7 +470,7 @@ def test_attention_prefill_tc(lens, hq, hkv, hd, page, window, splits):
         out = torch.full((len(rows), hq * hd), 7.0, dtype=torch.bfloat16, device=dev())
         ops.attention_prefill_tc(T(q, torch.bfloat16), case.k_pages, case.v_pages, out, T(np.array(tile0, dtype=np.int32)),
                                  T(np.array(tilen, dtype=np.int32)), len(tile0), pos, slot, case.table, hq, hkv, hd, window,
-                                 hd ** -0.5, splits, scratch, counters)
+                                 hd ** -0.5, splits, scratch, counters, alone=alone)
         assert ops.gemm_tc_status() == 0
         err = np.abs(N(out) - want).max(axis=1)
         assert err.max() <= 2.0 ** -7 * max(1.0, np.abs(want).max()), f"worst row {int(err.argmax())} of {len(rows)}: {rows[int(err.argmax())]}"
@@ -484,12 +489,17 @@ def test_attention_prefill_tc(lens, hq, hkv, hd, page, window, splits):
 def test_attention_prefill_tc_split_policy():
     """Few tiles of rows against many keys are split; a launch that fills the GPU by itself is not."""
     from machserve_b200 import ops
-    assert ops.attention_prefill_tc_splits(64, 14, 2, 64, 8192) == 1
-    assert ops.attention_prefill_tc_splits(4, 14, 2, 64, 2048) == 4
-    assert ops.attention_prefill_tc_splits(16, 14, 2, 64, 2048) == 1  # 224 blocks for 296 places
-    assert ops.attention_prefill_tc_splits(4, 12, 2, 128, 2048) == 4
-    assert ops.attention_prefill_tc_splits(4, 12, 2, 128, 512) == 1  # too few keys to split
-    assert ops.attention_prefill_tc_splits(1, 2, 1, 64, 1024) == 2
+    assert ops.attention_prefill_tc_plan(64, 14, 2, 64, 8192) == (1, False)
+    assert ops.attention_prefill_tc_plan(4, 14, 2, 64, 2048) == (4, False)
+    assert ops.attention_prefill_tc_plan(16, 14, 2, 64, 2048) == (1, False)  # 224 blocks for 296 places
+    # head size 128, by the model of the launch's time
+    assert ops.attention_prefill_tc_plan(64, 12, 2, 128, 8192, 2080) == (1, False)  # a long prompt whole: two heads a block
+    assert ops.attention_prefill_tc_plan(16, 12, 2, 128, 2048, 136) == (2, False)   # 96 blocks, the longest of 16 key tiles
+    assert ops.attention_prefill_tc_plan(32, 28, 4, 128, 4096) == (1, False)        # 512 blocks: nothing to gain
+    assert ops.attention_prefill_tc_plan(4, 28, 4, 128, 4096, 122) == (2, False)    # 64 blocks of equal length: 128, not 192
+    assert ops.attention_prefill_tc_plan(4, 12, 2, 128, 2048, 58) == (3, True)      # 24 blocks: 48 of one head, in 3 runs
+    assert ops.attention_prefill_tc_plan(4, 12, 2, 128, 512, 10) == (1, True)       # too few keys to split
+    assert ops.attention_prefill_tc_plan(1, 2, 1, 64, 1024) == (2, False)
 
 
 @pytest.mark.parametrize("k_gain", [None, 48.0])
