@@ -165,6 +165,57 @@ def free_device_memory():
 # ------------------------------------------------------------------------------------- one kernel alone
 
 
+def time_gemm_pair_tc(torch, ops, a, pk) -> int:
+    """The four products of a layer at `--prefill` rows: the repository's tcgen05 product with its fused epilogues (a
+    pair of SMs per tile; tests only, the engine multiplies with the library above 16 rows) beside the library's."""
+    raw = SHAPES[a.shape]
+    h, inter = raw["hidden_size"], raw["intermediate_size"]
+    hd = raw.get("head_dim", h // raw["num_attention_heads"])
+    qkv = (raw["num_attention_heads"] + 2 * raw["num_key_value_heads"]) * hd
+    m, dev = a.prefill, "cuda:0"
+    g = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *shape, s=0.05: (torch.randn(*shape, device=dev, generator=g) * s).to(torch.bfloat16)
+    x, xi = rnd(m, h, s=0.5), rnd(m, inter, s=0.5)
+    w_qkv, w_o, w_gu, w_d = rnd(qkv, h), rnd(h, h), rnd(2 * inter, h), rnd(h, inter, s=0.02)
+    res = torch.randn(m, h, device=dev, generator=g)
+    nb = ops.gemm_small_m_stats_blocks(h)
+    stats, copy = torch.ones(m, nb, device=dev), torch.empty(m, h, dtype=torch.bfloat16, device=dev)
+    o_qkv, o_h = torch.empty(m, qkv, dtype=torch.bfloat16, device=dev), torch.empty(m, h, dtype=torch.bfloat16, device=dev)
+    o_gu, o_i = torch.empty(m, 2 * inter, dtype=torch.bfloat16, device=dev), torch.empty(m, inter, dtype=torch.bfloat16, device=dev)
+
+    def us(fn, reps=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(reps):
+                fn()
+        graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (2 * reps) * 1000
+
+    out = {}
+    for name, own, lib, flops in (
+        ("qkv_norm_folded", lambda: ops.gemm_pair_tc(x, w_qkv, o_qkv, stats, nb, 1e-6), lambda: torch.mm(x, w_qkv.T, out=o_qkv), 2 * m * h * qkv),
+        ("o_residual_add", lambda: ops.gemm_pair_tc_resadd(x, w_o, res, stats, copy), lambda: torch.mm(x, w_o.T, out=o_h), 2 * m * h * h),
+        ("gate_up_silu_mul", lambda: ops.gemm_pair_tc_silu_mul(x, w_gu, o_i, stats, nb, 1e-6), lambda: torch.mm(x, w_gu.T, out=o_gu), 4 * m * h * inter),
+        ("down_residual_add", lambda: ops.gemm_pair_tc_resadd(xi, w_d, res, stats, copy), lambda: torch.mm(xi, w_d.T, out=o_h), 2 * m * h * inter)):
+        t_own, t_lib = us(own), us(lib)
+        out[name] = {"own_us": round(t_own, 1), "own_tflops": round(flops / t_own / 1e6), "library_us": round(t_lib, 1),
+                     "library_tflops": round(flops / t_lib / 1e6)}
+    assert ops.gemm_tc_status() == 0
+    print(json.dumps({"kernel": "gemm_pair_tc", "shape": a.shape, "rows": m, "dtype": "bf16", "products": out,
+                      "note": "own: with the epilogue named; library: the plain product alone", "peaks": pk["source"]}))
+    return 0
+
+
 def time_attention_prefill(torch, ops, a, pk) -> int:
     """The prompt attention kernel alone: one sequence of 2,048, 4,096 and 8,192 tokens attending to itself through
     the paged cache, replayed as a CUDA graph of ten launches; CUDA events around the replays."""
@@ -566,7 +617,7 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the further batch sizes and the prefill")
     ap.add_argument("--profile", default=None, choices=["decode", "prefill"],
                     help="which timed region is bracketed by cudaProfilerStart/Stop (for ncu --profile-from-start off)")
-    ap.add_argument("--kernel", default=None, choices=["attention_prefill"],
+    ap.add_argument("--kernel", default=None, choices=["attention_prefill", "gemm"],
                     help="time one kernel alone at the configuration's head sizes instead of the step, and print its own line")
     a = ap.parse_args()
 
@@ -588,6 +639,8 @@ def main() -> int:
     from machserve_b200 import ops
 
     pk = peaks()
+    if a.kernel == "gemm":
+        return time_gemm_pair_tc(torch, ops, a, pk)
     if a.kernel == "attention_prefill":
         return time_attention_prefill(torch, ops, a, pk)
     if a.model:

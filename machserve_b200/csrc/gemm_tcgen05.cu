@@ -930,3 +930,383 @@ MS_API int ms_gemm_rows_tc_resadd(const void* x, int ldx, const void* w, float* 
   ex.ldc = ldc;
   return rt_launch<RT_EPI_RESADD, 0>(x, ldx, w, nullptr, nullptr, 0, M, N, K, ex, sm_count, stream);
 }
+
+// ------------------------------------------------------------------------------------------------
+// The product for many rows with PAIRS of SMs on one tile (tcgen05 cta_group::2): a cluster of two resident blocks
+// goes through its tiles of the output one after the other.  A tile is 256 rows x BN columns (256, or 128 when that
+// leaves too few tiles); each block of the pair holds its own 128 rows of the activations and HALF of the tile's
+// weight rows in its shared memory, block 0 issues the instructions for both, and each block's tensor memory
+// receives the accumulators of its own 128 rows.  A block alone cannot feed the tensor core from its shared memory
+// (operand reads and TMA writes of a 128 x 256 tile add up to 192 bytes a cycle against the 128 it has); with the
+// weights split over the pair they fit.  K goes in steps of 64 through a ring of stages that runs on across tiles,
+// and there are TWO accumulators in tensor memory, so that the epilogue warps drain tile i while the tensor core
+// works on tile i + 1.  Tiles that share weight rows are neighbours in the order.
+// Both blocks copy with TMA into their own shared memory and count the bytes on block 0's barrier (no load uses
+// cluster multicast); block 0's commits reach both blocks' barriers; the epilogue threads of both blocks arrive on
+// block 0's barrier when they have drained an accumulator.  Every wait is bounded as above.
+// Epilogues as in the few-row kernels (gemm_small_m.cu), so that a pre-norm block needs no kernel between its
+// products:
+//   plain      out = acc (bfloat16)
+//   SCALE      every output row times 1 / rms of the row the activations were rounded from, made from the
+//              sums of squares that RESADD left: the RMS norm for a matrix with the norm's weight folded in
+//   SILU_MUL   block 0 holds BN/2 gate rows, block 1 the BN/2 up rows of the same outputs; out = silu(gate) * up
+//   RESADD     residual (float32) += acc in place; a bfloat16 copy of the new residual; its sums of squares
+//              per row and block of 16 columns
+#define PR_BK 64
+#define PR_THREADS 192
+#define PR_MAX_STAGES 8
+#define PR_PEER_MASK 0xFEFFFFFFu  // a shared::cluster address with this bit cleared is block 0's copy of the same place
+enum { PR_EPI_BF16 = 0, PR_EPI_SILU_MUL = 1, PR_EPI_RESADD = 2 };
+
+struct PrExtra {
+  const float* stats_in;  // SCALE: [M][stats_in_nb] sums of squares of the rows the activations were rounded from
+  int stats_in_nb;
+  float eps;
+  int up_offset;          // SILU_MUL: rows between a gate row and its up row in the weight matrix
+  float* residual;        // RESADD: float32 [M][ldr], added into in place
+  int ldr;
+  float* stats_out;       // RESADD: [M][stats_out_nb]
+  int stats_out_nb;
+  __nv_bfloat16* copy_out;  // RESADD, optional: [M][ldc]
+  int ldc;
+};
+
+struct PrShared {
+  unsigned long long full[PR_MAX_STAGES], empty[PR_MAX_STAGES], acc_full[2], acc_empty[2];
+  unsigned tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ unsigned pr_cluster_rank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void pr_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// A copy into this block's shared memory whose bytes are counted on block 0's barrier at the same place.
+__device__ __forceinline__ void pr_tma_load_2d(unsigned dst, const CUtensorMap* map, int c0, int c1, unsigned bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(dst),
+      "l"(map), "r"(c0), "r"(c1), "r"(bar & PR_PEER_MASK)
+      : "memory");
+}
+__device__ __forceinline__ void pr_mma(unsigned tmem, unsigned long long adesc, unsigned long long bdesc, unsigned idesc,
+                                       unsigned accumulate) {
+  const unsigned z = 0;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}\n" ::"r"(tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(z)
+      : "memory");
+}
+// When the instructions issued so far are done, one arrival on the barrier at this place in both blocks of the pair.
+__device__ __forceinline__ void pr_commit_both(unsigned bar) {
+  const unsigned short both = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n" ::"r"(bar),
+               "h"(both)
+               : "memory");
+}
+// 32 floats of a row, with 16-byte loads where the row allows it; what lies past `valid` reads as zero.
+__device__ __forceinline__ void pr_load32(float (&dst)[32], const float* src, int valid) {
+  if (valid >= 32 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+      const float4 r = *reinterpret_cast<const float4*>(src + i);
+      dst[i] = r.x; dst[i + 1] = r.y; dst[i + 2] = r.z; dst[i + 3] = r.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) dst[i] = i < valid ? src[i] : 0.f;
+  }
+}
+__device__ __forceinline__ void pr_arrive_block0(unsigned bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];\n" ::"r"(bar & PR_PEER_MASK) : "memory");
+}
+
+template <int BN, int EPI, int SCALE>
+__global__ void __launch_bounds__(PR_THREADS, 1)
+gemm_pair_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                    __nv_bfloat16* __restrict__ out, int ldo, int M, int N, int K, int tiles_m, int num_tiles, PrExtra ex) {
+  constexpr int HALF = BN / 2;                          // weight rows a block holds of a tile
+  constexpr int STAGE_BYTES = (128 + HALF) * PR_BK * 2;  // per block
+  constexpr int STAGES = BN == 256 ? 6 : 8;
+  constexpr int OUT_COLS = EPI == PR_EPI_SILU_MUL ? HALF : BN;  // output columns of a tile
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  PrShared* sh = reinterpret_cast<PrShared*>(tiles + STAGES * STAGE_BYTES);
+  volatile int* abort_flag = &sh->abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = (int)pr_cluster_rank();
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int kt_count = (K + PR_BK - 1) / PR_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      tc_mbar_init(tc_smem(&sh->full[s]), 1);   // block 0's: its own announcement of the bytes; both blocks' copies count on it
+      tc_mbar_init(tc_smem(&sh->empty[s]), 1);  // each block's own: block 0's commit arrives on both
+    }
+    for (int b = 0; b < 2; ++b) {
+      tc_mbar_init(tc_smem(&sh->acc_full[b]), 1);     // each block's own
+      tc_mbar_init(tc_smem(&sh->acc_empty[b]), 256);  // block 0's: the epilogue threads of both blocks
+    }
+    sh->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {  // the same warp of both blocks: the accumulators of a pair lie at the same columns
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem(&sh->tmem_base)),
+                 "r"(2 * BN)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  pr_cluster_sync();  // the other block's barriers exist before anything arrives on them
+  tc_fence_after();
+  const unsigned tmem = sh->tmem_base;
+
+  if (warp == 0 && lane == 0) {
+    // producer (both blocks): the ring of stages runs on from tile to tile
+    int it = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      const int mt = tile % tiles_m, nt = tile / tiles_m;
+      const int m0 = mt * 256 + rank * 128;
+      const int w0 = EPI == PR_EPI_SILU_MUL ? nt * HALF + rank * ex.up_offset : nt * BN + rank * HALF;
+      for (int kt = 0; kt < kt_count; ++kt, ++it) {
+        const int s = it % STAGES;
+        if (it >= STAGES && !tc_mbar_wait(tc_smem(&sh->empty[s]), ((it / STAGES) - 1) & 1, abort_flag, 21)) {
+          ok = false;
+          break;
+        }
+        const unsigned a_dst = tc_smem(tiles + s * STAGE_BYTES);
+        const unsigned b_dst = a_dst + 128 * PR_BK * 2;
+        const unsigned bar = tc_smem(&sh->full[s]);
+        if (rank == 0) tc_mbar_expect_tx(bar, 2 * STAGE_BYTES);
+        pr_tma_load_2d(a_dst, &map_x, kt * PR_BK, m0, bar);
+        pr_tma_load_2d(b_dst, &map_w, kt * PR_BK, w0, bar);
+      }
+    }
+  } else if (warp == 1 && lane == 0 && rank == 0) {
+    // issuer (block 0): four K = 16 instructions of 256 x BN per stage, into the accumulator both epilogues have drained
+    const unsigned idesc = tc_instr_desc(256, BN);
+    int it = 0, count = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++count) {
+      const int buf = count & 1;
+      if (count >= 2) {
+        ok = tc_mbar_wait(tc_smem(&sh->acc_empty[buf]), ((count >> 1) - 1) & 1, abort_flag, 22);
+        if (!ok) break;
+        tc_fence_after();
+      }
+      const unsigned acc = tmem + buf * BN;
+      for (int kt = 0; kt < kt_count; ++kt, ++it) {
+        const int s = it % STAGES;
+        ok = tc_mbar_wait(tc_smem(&sh->full[s]), (it / STAGES) & 1, abort_flag, 22);
+        if (!ok) break;
+        tc_fence_after();
+        const unsigned a_src = tc_smem(tiles + s * STAGE_BYTES);
+        const unsigned b_src = a_src + 128 * PR_BK * 2;
+#pragma unroll
+        for (int k = 0; k < PR_BK / 16; ++k)
+          pr_mma(acc, tc_smem_desc(a_src + k * 32), tc_smem_desc(b_src + k * 32), idesc, (kt | k) != 0);
+        pr_commit_both(tc_smem(&sh->empty[s]));
+      }
+      if (ok) pr_commit_both(tc_smem(&sh->acc_full[buf]));
+    }
+  } else if (warp >= 2) {
+    // epilogue (both blocks): thread = row of the block's half of the tile; a warp may touch the 32 lanes of tensor
+    // memory that its number allows
+    const int group = warp & 3;
+    int count = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++count) {
+      const int mt = tile % tiles_m, nt = tile / tiles_m;
+      const int m = mt * 256 + rank * 128 + group * 32 + lane, n0 = nt * OUT_COLS;
+      const bool row_ok = m < M;
+      float inv = 1.f;
+      if (SCALE && row_ok) {  // while the tensor core still works on the tile
+        float ss = 0.f;
+        for (int b = 0; b < ex.stats_in_nb; ++b) ss += ex.stats_in[(size_t)m * ex.stats_in_nb + b];
+        inv = rsqrtf(ss / (float)K + ex.eps);
+      }
+      float rnext[32];  // RESADD: the old residual of the chunk to come, requested a chunk ahead
+      if (EPI == PR_EPI_RESADD) pr_load32(rnext, ex.residual + (size_t)(row_ok ? m : 0) * ex.ldr + n0, row_ok ? N - n0 : 0);
+      const int buf = count & 1;
+      ok = tc_mbar_wait(tc_smem(&sh->acc_full[buf]), (count >> 1) & 1, abort_flag, 23);
+      if (!ok) break;
+      tc_fence_after();
+      const unsigned row_addr = tmem + buf * BN + ((unsigned)(group * 32) << 16);
+      if (EPI == PR_EPI_SILU_MUL) {
+#pragma unroll 1
+        for (int c = 0; c < OUT_COLS; c += 32) {
+          float g[32], u[32];
+          tc_ld32(row_addr + c, g);
+          tc_ld32(row_addr + OUT_COLS + c, u);
+          if (row_ok && n0 + c < N) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float gate = g[i] * inv;
+              g[i] = gate / (1.f + __expf(-gate)) * (u[i] * inv);
+            }
+            tc_store_row_bf16(out + (size_t)m * ldo + n0 + c, g, N - n0 - c);
+          }
+        }
+      } else if (EPI == PR_EPI_RESADD) {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          float v[32];
+          tc_ld32(row_addr + c, v);
+          const int n = n0 + c, valid = N - n;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = i < valid ? v[i] + rnext[i] : 0.f;
+          if (c + 32 < BN) pr_load32(rnext, ex.residual + (size_t)(row_ok ? m : 0) * ex.ldr + n + 32, row_ok ? valid - 32 : 0);
+          if (row_ok && valid > 0) {
+            float* res = ex.residual + (size_t)m * ex.ldr + n;
+            if (valid >= 32 && (reinterpret_cast<uintptr_t>(res) & 15) == 0) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(res + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (i < valid) res[i] = v[i];
+            }
+            if (ex.copy_out) tc_store_row_bf16(ex.copy_out + (size_t)m * ex.ldc + n, v, valid);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              if (16 * h < valid) {
+                float ss = 0.f;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) ss += v[16 * h + i] * v[16 * h + i];
+                ex.stats_out[(size_t)m * ex.stats_out_nb + n / 16 + h] = ss;
+              }
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          float v[32];
+          tc_ld32(row_addr + c, v);
+          if (row_ok && n0 + c < N) {
+            if (SCALE) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] *= inv;
+            }
+            tc_store_row_bf16(out + (size_t)m * ldo + n0 + c, v, N - n0 - c);
+          }
+        }
+      }
+      tc_fence_before();
+      pr_arrive_block0(tc_smem(&sh->acc_empty[buf]));
+    }
+  }
+  // leave together: neither block's shared memory, barriers or tensor memory may go while the other still uses them
+  tc_fence_before();
+  __syncthreads();
+  pr_cluster_sync();
+  if (*abort_flag) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(2 * BN) : "memory");
+  }
+}
+
+template <int BN, int EPI, int SCALE>
+static int pr_launch(const CUtensorMap& mx, const CUtensorMap& mw, void* out, int ldo, int M, int N, int K, const PrExtra& ex,
+                     int sm_count, cudaStream_t stream) {
+  constexpr int STAGES = BN == 256 ? 6 : 8;
+  const size_t smem = (size_t)STAGES * (128 + BN / 2) * PR_BK * 2 + sizeof(PrShared) + 1024;
+  auto kern = gemm_pair_tc_kernel<BN, EPI, SCALE>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) {
+      ms_set_error("gemm_pair_tc: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+      return 2;
+    }
+    configured = true;
+  }
+  constexpr int OUT_COLS = EPI == PR_EPI_SILU_MUL ? BN / 2 : BN;
+  const int tiles_m = (M + 255) / 256, tiles_n = (N + OUT_COLS - 1) / OUT_COLS;
+  const int num_tiles = tiles_m * tiles_n;
+  const int pairs = num_tiles < sm_count / 2 ? num_tiles : sm_count / 2;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(PR_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  MS_LAUNCH_RESULT("gemm_pair_tc", cudaLaunchKernelEx(&cfg, kern, mx, mw, (__nv_bfloat16*)out, ldo, M, N, K, tiles_m, num_tiles, ex));
+  return 0;
+}
+
+// Tiles of 256 columns when they give the pairs of SMs about as much to do as tiles of 128 would (the tensor core is fed
+// fully only by the wide ones).
+static bool pr_wide(int M, int N, int sm_count) {
+  const long long tm = (M + 255) / 256;
+  return tm * ((N + 255) / 256) >= (long long)(sm_count / 2) * 9 / 10;
+}
+
+static int pr_maps(CUtensorMap* mx, CUtensorMap* mw, const void* x, int ldx, const void* w, int M, int w_rows, int K, int w_box) {
+  MS_REQUIRE(M >= 1 && w_rows >= 1 && K >= 8 && K % 8 == 0, "gemm_pair_tc: M=%d N=%d K=%d (a multiple of 8) is not covered", M, w_rows, K);
+  MS_REQUIRE(ldx % 8 == 0 && ldx >= K && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0),
+             "gemm_pair_tc: operands must be 16-byte aligned with row strides that are multiples of 8");
+  if (int rc = tc_make_map(mx, x, M, K, ldx, 128)) return rc;
+  return tc_make_map(mw, w, w_rows, K, K, w_box);
+}
+
+// out[M, N] = x[M, K] . w[N, K]^T, all bfloat16.  stats_in (or null): [M][stats_nb] sums of squares of the rows that
+// x was rounded from; every output row is then divided by that row's rms (K values, eps inside the root).
+MS_API int ms_gemm_pair_tc(const void* x, int ldx, const void* w, void* out, int ldo, int M, int N, int K,
+                           const float* stats_in, int stats_nb, float eps, int sm_count, cudaStream_t stream) {
+  if (M == 0) return 0;
+  MS_REQUIRE(ldo >= N && sm_count >= 2 && (stats_in == nullptr || stats_nb >= 1), "gemm_pair_tc: bad sizes ldo=%d", ldo);
+  const bool wide = pr_wide(M, N, sm_count);
+  CUtensorMap mx, mw;
+  if (int rc = pr_maps(&mx, &mw, x, ldx, w, M, N, K, wide ? 128 : 64)) return rc;
+  PrExtra ex = {stats_in, stats_nb, eps, 0, nullptr, 0, nullptr, 0, nullptr, 0};
+  if (stats_in)
+    return wide ? pr_launch<256, PR_EPI_BF16, 1>(mx, mw, out, ldo, M, N, K, ex, sm_count, stream)
+                : pr_launch<128, PR_EPI_BF16, 1>(mx, mw, out, ldo, M, N, K, ex, sm_count, stream);
+  return wide ? pr_launch<256, PR_EPI_BF16, 0>(mx, mw, out, ldo, M, N, K, ex, sm_count, stream)
+              : pr_launch<128, PR_EPI_BF16, 0>(mx, mw, out, ldo, M, N, K, ex, sm_count, stream);
+}
+
+// out[M, I] = silu(x . w[0:I]^T) * (x . w[I:2I]^T); w is [2I, K] with the gate rows first; row scaling as above.
+MS_API int ms_gemm_pair_tc_silu_mul(const void* x, int ldx, const void* w_gate_up, void* out, int ldo, int M, int I, int K,
+                                    const float* stats_in, int stats_nb, float eps, int sm_count, cudaStream_t stream) {
+  if (M == 0) return 0;
+  MS_REQUIRE(ldo >= I && sm_count >= 2 && (stats_in == nullptr || stats_nb >= 1), "gemm_pair_tc_silu_mul: bad sizes ldo=%d", ldo);
+  CUtensorMap mx, mw;
+  if (int rc = pr_maps(&mx, &mw, x, ldx, w_gate_up, M, 2 * I, K, 128)) return rc;
+  PrExtra ex = {stats_in, stats_nb, eps, I, nullptr, 0, nullptr, 0, nullptr, 0};
+  if (stats_in) return pr_launch<256, PR_EPI_SILU_MUL, 1>(mx, mw, out, ldo, M, I, K, ex, sm_count, stream);
+  return pr_launch<256, PR_EPI_SILU_MUL, 0>(mx, mw, out, ldo, M, I, K, ex, sm_count, stream);
+}
+
+// residual[M, N] (float32) += x[M, K] . w[N, K]^T in place; stats_out[m][b] = the sum of squares of the new
+// residual's row m over its b-th block of 16 columns ((N + 15) / 16 blocks a row); copy_out (or null): the new
+// residual rounded to bfloat16.
+MS_API int ms_gemm_pair_tc_resadd(const void* x, int ldx, const void* w, float* residual, int ldr, float* stats_out,
+                                  void* copy_out, int ldc, int M, int N, int K, int sm_count, cudaStream_t stream) {
+  if (M == 0) return 0;
+  MS_REQUIRE(residual != nullptr && stats_out != nullptr && ldr >= N && sm_count >= 2 && (copy_out == nullptr || ldc >= N),
+             "gemm_pair_tc_resadd: bad sizes ldr=%d ldc=%d", ldr, ldc);
+  const bool wide = pr_wide(M, N, sm_count);
+  CUtensorMap mx, mw;
+  if (int rc = pr_maps(&mx, &mw, x, ldx, w, M, N, K, wide ? 128 : 64)) return rc;
+  PrExtra ex = {nullptr, 0, 0.f, 0, residual, ldr, stats_out, (N + 15) / 16, (__nv_bfloat16*)copy_out, ldc};
+  return wide ? pr_launch<256, PR_EPI_RESADD, 0>(mx, mw, nullptr, 0, M, N, K, ex, sm_count, stream)
+              : pr_launch<128, PR_EPI_RESADD, 0>(mx, mw, nullptr, 0, M, N, K, ex, sm_count, stream);
+}

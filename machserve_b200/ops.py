@@ -88,6 +88,9 @@ class _Signatures:
     ms_gemm_rows_tc_silu_mul = [P, I, P, P, P, I, I, I, I, I, P]
     ms_gemm_rows_tc_scaled = [P, I, P, I, F, P, P, P, I, I, I, I, I, P]
     ms_gemm_rows_tc_resadd = [P, I, P, P, I, P, P, I, I, I, I, I, P]
+    ms_gemm_pair_tc = [P, I, P, P, I, I, I, I, P, I, F, I, P]
+    ms_gemm_pair_tc_silu_mul = [P, I, P, P, I, I, I, I, P, I, F, I, P]
+    ms_gemm_pair_tc_resadd = [P, I, P, P, I, P, P, I, I, I, I, I, P]
     ms_gemm_tc_wait_probe = [I, P]
     ms_attention_tc_wait_probe = [I, P]
     ms_take_sampled_tokens = [P, P, P, I, I, P]
@@ -648,9 +651,59 @@ def gemm_rows_tc_scaled(x, stats, stats_blocks, eps, w, w_up, out):
     return out
 
 
+def gemm_pair_tc(x, w, out, stats=None, stats_blocks=0, eps=0.0):
+    """out[M, N] = x[M, K] . w[N, K]^T for many rows on the tcgen05 tensor cores (a pair of SMs per tile, resident
+    blocks that go through their tiles, two accumulators in tensor memory), all bfloat16.  With `stats` ([M, stats_blocks] sums of
+    squares of the rows x was rounded from) every output row is divided by that row's rms: the RMS norm for a matrix
+    with the norm's weight folded into its columns."""
+    m, k = x.shape
+    n = w.shape[0]
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype == torch.bfloat16, "gemm_pair_tc: bfloat16 only")
+    _need(w.is_contiguous() and w.shape[1] == k and x.stride(1) == 1 and out.stride(1) == 1 and tuple(out.shape) == (m, n),
+          "gemm_pair_tc: bad layout")
+    _need(stats is None or (stats.dtype == torch.float32 and stats.is_contiguous() and stats.numel() >= m * stats_blocks >= m),
+          "gemm_pair_tc: bad stats buffer")
+    _check(lib().ms_gemm_pair_tc(_ptr(x), x.stride(0), _ptr(w), _ptr(out), out.stride(0), m, n, k, _ptr(stats), int(stats_blocks),
+                                   float(eps), sm_count(), _stream()), "gemm_pair_tc")
+    return out
+
+
+def gemm_pair_tc_silu_mul(x, w_gate_up, out, stats=None, stats_blocks=0, eps=0.0):
+    """out[M, I] = silu(x . w_gate^T) * (x . w_up^T) with w_gate_up = [gate rows; up rows] ([2I, K]); row scaling as in
+    gemm_pair_tc."""
+    m, k = x.shape
+    i = w_gate_up.shape[0] // 2
+    _need(x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and out.dtype == torch.bfloat16, "gemm_pair_tc_silu_mul: bfloat16 only")
+    _need(w_gate_up.is_contiguous() and w_gate_up.shape[1] == k and w_gate_up.shape[0] == 2 * i and x.stride(1) == 1 and
+          out.stride(1) == 1 and tuple(out.shape) == (m, i), "gemm_pair_tc_silu_mul: bad layout")
+    _need(stats is None or (stats.dtype == torch.float32 and stats.is_contiguous() and stats.numel() >= m * stats_blocks >= m),
+          "gemm_pair_tc_silu_mul: bad stats buffer")
+    _check(lib().ms_gemm_pair_tc_silu_mul(_ptr(x), x.stride(0), _ptr(w_gate_up), _ptr(out), out.stride(0), m, i, k, _ptr(stats),
+                                            int(stats_blocks), float(eps), sm_count(), _stream()), "gemm_pair_tc_silu_mul")
+    return out
+
+
+def gemm_pair_tc_resadd(x, w, residual, stats_out, copy_out=None):
+    """residual[M, N] += x[M, K] . w[N, K]^T in place (float32), the sums of squares of the new residual per row and
+    block of 16 columns (as gemm_small_m_resadd leaves them), and optionally its bfloat16 copy; any number of rows."""
+    m, k = x.shape
+    n = w.shape[0]
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and residual.dtype == torch.float32, "gemm_pair_tc_resadd: bad dtypes")
+    _need(w.is_contiguous() and w.shape[1] == k and x.stride(1) == 1 and residual.stride(1) == 1, "gemm_pair_tc_resadd: bad layout")
+    _need(tuple(residual.shape) == (m, n), "gemm_pair_tc_resadd: the residual must be [rows, N]")
+    _need(stats_out.dtype == torch.float32 and stats_out.is_contiguous() and stats_out.numel() >= m * gemm_small_m_stats_blocks(n),
+          "gemm_pair_tc_resadd: bad stats buffer")
+    _need(copy_out is None or (copy_out.dtype == torch.bfloat16 and tuple(copy_out.shape) == (m, n) and copy_out.stride(1) == 1),
+          "gemm_pair_tc_resadd: the copy must be bfloat16 [rows, N]")
+    _check(lib().ms_gemm_pair_tc_resadd(_ptr(x), x.stride(0), _ptr(w), _ptr(residual), residual.stride(0), _ptr(stats_out),
+                                          _ptr(copy_out), copy_out.stride(0) if copy_out is not None else 0, m, n, k, sm_count(),
+                                          _stream()), "gemm_pair_tc_resadd")
+    return residual
+
+
 def gemm_tc_status(reset: bool = True) -> int:
-    """0, or which bounded wait of a tcgen05 kernel gave up (products: 1 producer, 2 issuer, 3 epilogue;
-    attention: 11 producer, 12-14 and 16 issuer, 15 softmax threads).  Synchronizes."""
+    """0, or which bounded wait of a tcgen05 kernel gave up (products: 1 producer, 2 issuer, 3 epilogue, 21-23 the same of the
+    resident-block product; attention: 11 producer, 12-14 and 16 issuer, 15 softmax threads).  Synchronizes."""
     codes = tc_status_codes(reset)
     return codes[0] or codes[1]
 
