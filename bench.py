@@ -178,7 +178,7 @@ def time_gemm_pair_tc(torch, ops, a, pk) -> int:
     x, xi = rnd(m, h, s=0.5), rnd(m, inter, s=0.5)
     w_qkv, w_o, w_gu, w_d = rnd(qkv, h), rnd(h, h), rnd(2 * inter, h), rnd(h, inter, s=0.02)
     res = torch.randn(m, h, device=dev, generator=g)
-    nb = ops.gemm_small_m_stats_blocks(h)
+    nb = ops.gemm_pair_tc_stats_blocks(m, h)
     stats, copy = torch.ones(m, nb, device=dev), torch.empty(m, h, dtype=torch.bfloat16, device=dev)
     o_qkv, o_h = torch.empty(m, qkv, dtype=torch.bfloat16, device=dev), torch.empty(m, h, dtype=torch.bfloat16, device=dev)
     o_gu, o_i = torch.empty(m, 2 * inter, dtype=torch.bfloat16, device=dev), torch.empty(m, inter, dtype=torch.bfloat16, device=dev)

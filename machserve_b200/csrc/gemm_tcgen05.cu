@@ -951,10 +951,11 @@ MS_API int ms_gemm_rows_tc_resadd(const void* x, int ldx, const void* w, float* 
 //              sums of squares that RESADD left: the RMS norm for a matrix with the norm's weight folded in
 //   SILU_MUL   block 0 holds BN/2 gate rows, block 1 the BN/2 up rows of the same outputs; out = silu(gate) * up
 //   RESADD     residual (float32) += acc in place; a bfloat16 copy of the new residual; its sums of squares
-//              per row and block of 16 columns
+//              per row and tile of columns (a consumer adds up all of a row's sums, however many there are)
 #define PR_BK 64
 #define PR_THREADS 192
 #define PR_MAX_STAGES 8
+#define PR_STAGE_BYTES_PER_WARP (32 * 144)  // where a warp's 32 rows x 32 columns change hands in the epilogue
 #define PR_PEER_MASK 0xFEFFFFFFu  // a shared::cluster address with this bit cleared is block 0's copy of the same place
 enum { PR_EPI_BF16 = 0, PR_EPI_SILU_MUL = 1, PR_EPI_RESADD = 2 };
 
@@ -1117,86 +1118,118 @@ gemm_pair_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       if (ok) pr_commit_both(tc_smem(&sh->acc_full[buf]));
     }
   } else if (warp >= 2) {
-    // epilogue (both blocks): thread = row of the block's half of the tile; a warp may touch the 32 lanes of tensor
-    // memory that its number allows
+    // epilogue (both blocks).  A warp may touch the 32 lanes of tensor memory that its number allows: it takes 32 rows
+    // of the block's half of the tile, 32 columns at a time, a row per thread; the values then change hands through
+    // the warp's piece of shared memory so that a thread holds consecutive columns of few rows and global memory is
+    // read and written in whole rows of the chunk (a row per thread would cost a transaction per thread and access).
     const int group = warp & 3;
+    unsigned char* stage = reinterpret_cast<unsigned char*>(sh) + 1024 + (warp - 2) * PR_STAGE_BYTES_PER_WARP;
     int count = 0;
     bool ok = true;
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++count) {
       const int mt = tile % tiles_m, nt = tile / tiles_m;
-      const int m = mt * 256 + rank * 128 + group * 32 + lane, n0 = nt * OUT_COLS;
-      const bool row_ok = m < M;
+      const int m_warp = mt * 256 + rank * 128 + group * 32;  // the warp's first row
+      const int m = m_warp + lane, n0 = nt * OUT_COLS;
       float inv = 1.f;
-      if (SCALE && row_ok) {  // while the tensor core still works on the tile
-        float ss = 0.f;
-        for (int b = 0; b < ex.stats_in_nb; ++b) ss += ex.stats_in[(size_t)m * ex.stats_in_nb + b];
-        inv = rsqrtf(ss / (float)K + ex.eps);
+      if (SCALE && m < M) {  // while the tensor core still works on the tile; eight loads in flight at a time
+        const float* st = ex.stats_in + (size_t)m * ex.stats_in_nb;
+        float part[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int b = 0; b < ex.stats_in_nb; b += 8) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) part[i] += b + i < ex.stats_in_nb ? st[b + i] : 0.f;
+        }
+        inv = rsqrtf((((part[0] + part[1]) + (part[2] + part[3])) + ((part[4] + part[5]) + (part[6] + part[7]))) / (float)K + ex.eps);
       }
-      float rnext[32];  // RESADD: the old residual of the chunk to come, requested a chunk ahead
-      if (EPI == PR_EPI_RESADD) pr_load32(rnext, ex.residual + (size_t)(row_ok ? m : 0) * ex.ldr + n0, row_ok ? N - n0 : 0);
+      // RESADD, after the exchange: thread = (row 4 i + lane / 8, columns 4 (lane % 8) .. + 3) for i = 0 .. 7
+      const int rr = lane >> 3, rq = lane & 7;
+      float4 rold[8];  // the old residual of the chunk to come, requested a chunk ahead
+      float ss[8];     // sums of squares of the new residual, per row of this thread, over the tile
+      if (EPI == PR_EPI_RESADD) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          ss[i] = 0.f;
+          const int row = m_warp + 4 * i + rr, col = n0 + 4 * rq;
+          rold[i] = (row < M && col < N) ? *reinterpret_cast<const float4*>(ex.residual + (size_t)row * ex.ldr + col) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
       const int buf = count & 1;
       ok = tc_mbar_wait(tc_smem(&sh->acc_full[buf]), (count >> 1) & 1, abort_flag, 23);
       if (!ok) break;
       tc_fence_after();
       const unsigned row_addr = tmem + buf * BN + ((unsigned)(group * 32) << 16);
-      if (EPI == PR_EPI_SILU_MUL) {
 #pragma unroll 1
-        for (int c = 0; c < OUT_COLS; c += 32) {
-          float g[32], u[32];
-          tc_ld32(row_addr + c, g);
+      for (int c = 0; c < OUT_COLS; c += 32) {
+        float v[32];
+        tc_ld32(row_addr + c, v);
+        if (EPI == PR_EPI_SILU_MUL) {
+          float u[32];
           tc_ld32(row_addr + OUT_COLS + c, u);
-          if (row_ok && n0 + c < N) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const float gate = g[i] * inv;
-              g[i] = gate / (1.f + __expf(-gate)) * (u[i] * inv);
-            }
-            tc_store_row_bf16(out + (size_t)m * ldo + n0 + c, g, N - n0 - c);
+          for (int i = 0; i < 32; ++i) {
+            const float gate = v[i] * inv;
+            v[i] = gate * __frcp_rn(1.f + __expf(-gate)) * (u[i] * inv);  // (a reciprocal of infinity is zero: no NaN far left)
           }
+        } else if (SCALE) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] *= inv;
         }
-      } else if (EPI == PR_EPI_RESADD) {
-#pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
-          float v[32];
-          tc_ld32(row_addr + c, v);
-          const int n = n0 + c, valid = N - n;
+        const int n = n0 + c;
+        if (EPI == PR_EPI_RESADD) {
+          // float32 through the exchange: rows of 144 bytes (16-byte accesses of a quarter warp fall into different banks)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = i < valid ? v[i] + rnext[i] : 0.f;
-          if (c + 32 < BN) pr_load32(rnext, ex.residual + (size_t)(row_ok ? m : 0) * ex.ldr + n + 32, row_ok ? valid - 32 : 0);
-          if (row_ok && valid > 0) {
-            float* res = ex.residual + (size_t)m * ex.ldr + n;
-            if (valid >= 32 && (reinterpret_cast<uintptr_t>(res) & 15) == 0) {
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<float4*>(stage + lane * 144 + 16 * j) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          __syncwarp();
 #pragma unroll
-              for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(res + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (i < valid) res[i] = v[i];
-            }
-            if (ex.copy_out) tc_store_row_bf16(ex.copy_out + (size_t)m * ex.ldc + n, v, valid);
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              if (16 * h < valid) {
-                float ss = 0.f;
-#pragma unroll
-                for (int i = 0; i < 16; ++i) ss += v[16 * h + i] * v[16 * h + i];
-                ex.stats_out[(size_t)m * ex.stats_out_nb + n / 16 + h] = ss;
+          for (int i = 0; i < 8; ++i) {
+            const int row = m_warp + 4 * i + rr, col = n + 4 * rq;
+            const float4 acc = *reinterpret_cast<const float4*>(stage + (4 * i + rr) * 144 + 16 * rq);
+            const float4 old = rold[i];
+            if (c + 32 < OUT_COLS)
+              rold[i] = (row < M && col + 32 < N) ? *reinterpret_cast<const float4*>(ex.residual + (size_t)row * ex.ldr + col + 32)
+                                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (row < M && col < N) {
+              const float4 nw = make_float4(old.x + acc.x, old.y + acc.y, old.z + acc.z, old.w + acc.w);
+              *reinterpret_cast<float4*>(ex.residual + (size_t)row * ex.ldr + col) = nw;
+              if (ex.copy_out) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(nw.x, nw.y), hi = __floats2bfloat162_rn(nw.z, nw.w);
+                *reinterpret_cast<uint2*>(ex.copy_out + (size_t)row * ex.ldc + col) =
+                    make_uint2(*reinterpret_cast<unsigned*>(&lo), *reinterpret_cast<unsigned*>(&hi));
               }
+              ss[i] += (nw.x * nw.x + nw.y * nw.y) + (nw.z * nw.z + nw.w * nw.w);
             }
           }
-        }
-      } else {
-#pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
-          float v[32];
-          tc_ld32(row_addr + c, v);
-          if (row_ok && n0 + c < N) {
-            if (SCALE) {
+          __syncwarp();
+        } else {
+          // bfloat16 through the exchange: rows of 80 bytes
 #pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] *= inv;
-            }
-            tc_store_row_bf16(out + (size_t)m * ldo + n0 + c, v, N - n0 - c);
+          for (int j = 0; j < 4; ++j) {
+            uint4 pk;
+            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(v[8 * j + 2 * e], v[8 * j + 2 * e + 1]);
+            *reinterpret_cast<uint4*>(stage + lane * 80 + 16 * j) = pk;
           }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int row = m_warp + 8 * i + (lane >> 2), col = n + 8 * (lane & 3);
+            const uint4 pk = *reinterpret_cast<const uint4*>(stage + (8 * i + (lane >> 2)) * 80 + 16 * (lane & 3));
+            if (row < M && col < N) *reinterpret_cast<uint4*>(out + (size_t)row * ldo + col) = pk;
+          }
+          __syncwarp();
+        }
+      }
+      if (EPI == PR_EPI_RESADD) {
+        // a row's eight threads add up their sums (in a fixed order) and one of them writes the row's sum for this tile
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float t = ss[i];
+          t += __shfl_xor_sync(0xffffffffu, t, 1);
+          t += __shfl_xor_sync(0xffffffffu, t, 2);
+          t += __shfl_xor_sync(0xffffffffu, t, 4);
+          const int row = m_warp + 4 * i + rr;
+          if (rq == 0 && row < M) ex.stats_out[(size_t)row * ex.stats_out_nb + nt] = t;
         }
       }
       tc_fence_before();
@@ -1220,7 +1253,7 @@ template <int BN, int EPI, int SCALE>
 static int pr_launch(const CUtensorMap& mx, const CUtensorMap& mw, void* out, int ldo, int M, int N, int K, const PrExtra& ex,
                      int sm_count, cudaStream_t stream) {
   constexpr int STAGES = BN == 256 ? 6 : 8;
-  const size_t smem = (size_t)STAGES * (128 + BN / 2) * PR_BK * 2 + sizeof(PrShared) + 1024;
+  const size_t smem = (size_t)STAGES * (128 + BN / 2) * PR_BK * 2 + 1024 + 4 * PR_STAGE_BYTES_PER_WARP + 1024;
   auto kern = gemm_pair_tc_kernel<BN, EPI, SCALE>;
   static bool configured = false;
   if (!configured) {
@@ -1259,7 +1292,8 @@ static bool pr_wide(int M, int N, int sm_count) {
 }
 
 static int pr_maps(CUtensorMap* mx, CUtensorMap* mw, const void* x, int ldx, const void* w, int M, int w_rows, int K, int w_box) {
-  MS_REQUIRE(M >= 1 && w_rows >= 1 && K >= 8 && K % 8 == 0, "gemm_pair_tc: M=%d N=%d K=%d (a multiple of 8) is not covered", M, w_rows, K);
+  MS_REQUIRE(M >= 1 && w_rows >= 8 && w_rows % 8 == 0 && K >= 8 && K % 8 == 0,
+             "gemm_pair_tc: M=%d N=%d K=%d (N and K multiples of 8) is not covered", M, w_rows, K);
   MS_REQUIRE(ldx % 8 == 0 && ldx >= K && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0),
              "gemm_pair_tc: operands must be 16-byte aligned with row strides that are multiples of 8");
   if (int rc = tc_make_map(mx, x, M, K, ldx, 128)) return rc;
@@ -1271,7 +1305,8 @@ static int pr_maps(CUtensorMap* mx, CUtensorMap* mw, const void* x, int ldx, con
 MS_API int ms_gemm_pair_tc(const void* x, int ldx, const void* w, void* out, int ldo, int M, int N, int K,
                            const float* stats_in, int stats_nb, float eps, int sm_count, cudaStream_t stream) {
   if (M == 0) return 0;
-  MS_REQUIRE(ldo >= N && sm_count >= 2 && (stats_in == nullptr || stats_nb >= 1), "gemm_pair_tc: bad sizes ldo=%d", ldo);
+  MS_REQUIRE(ldo >= N && ldo % 8 == 0 && (uintptr_t)out % 16 == 0 && sm_count >= 2 && (stats_in == nullptr || stats_nb >= 1),
+             "gemm_pair_tc: bad sizes ldo=%d (a multiple of 8, rows 16-byte aligned)", ldo);
   const bool wide = pr_wide(M, N, sm_count);
   CUtensorMap mx, mw;
   if (int rc = pr_maps(&mx, &mw, x, ldx, w, M, N, K, wide ? 128 : 64)) return rc;
@@ -1287,7 +1322,8 @@ MS_API int ms_gemm_pair_tc(const void* x, int ldx, const void* w, void* out, int
 MS_API int ms_gemm_pair_tc_silu_mul(const void* x, int ldx, const void* w_gate_up, void* out, int ldo, int M, int I, int K,
                                     const float* stats_in, int stats_nb, float eps, int sm_count, cudaStream_t stream) {
   if (M == 0) return 0;
-  MS_REQUIRE(ldo >= I && sm_count >= 2 && (stats_in == nullptr || stats_nb >= 1), "gemm_pair_tc_silu_mul: bad sizes ldo=%d", ldo);
+  MS_REQUIRE(ldo >= I && ldo % 8 == 0 && I % 8 == 0 && (uintptr_t)out % 16 == 0 && sm_count >= 2 && (stats_in == nullptr || stats_nb >= 1),
+             "gemm_pair_tc_silu_mul: bad sizes I=%d ldo=%d (multiples of 8, rows 16-byte aligned)", I, ldo);
   CUtensorMap mx, mw;
   if (int rc = pr_maps(&mx, &mw, x, ldx, w_gate_up, M, 2 * I, K, 128)) return rc;
   PrExtra ex = {stats_in, stats_nb, eps, I, nullptr, 0, nullptr, 0, nullptr, 0};
@@ -1295,18 +1331,22 @@ MS_API int ms_gemm_pair_tc_silu_mul(const void* x, int ldx, const void* w_gate_u
   return pr_launch<256, PR_EPI_SILU_MUL, 0>(mx, mw, out, ldo, M, I, K, ex, sm_count, stream);
 }
 
+// How many sums of squares a row of ms_gemm_pair_tc_resadd's stats_out has (one per tile of columns).
+MS_API int ms_gemm_pair_tc_stats_blocks(int M, int N, int sm_count) { return pr_wide(M, N, sm_count) ? (N + 255) / 256 : (N + 127) / 128; }
+
 // residual[M, N] (float32) += x[M, K] . w[N, K]^T in place; stats_out[m][b] = the sum of squares of the new
-// residual's row m over its b-th block of 16 columns ((N + 15) / 16 blocks a row); copy_out (or null): the new
-// residual rounded to bfloat16.
+// residual's row m over its b-th tile of columns (ms_gemm_pair_tc_stats_blocks of them a row); copy_out (or null):
+// the new residual rounded to bfloat16.
 MS_API int ms_gemm_pair_tc_resadd(const void* x, int ldx, const void* w, float* residual, int ldr, float* stats_out,
                                   void* copy_out, int ldc, int M, int N, int K, int sm_count, cudaStream_t stream) {
   if (M == 0) return 0;
-  MS_REQUIRE(residual != nullptr && stats_out != nullptr && ldr >= N && sm_count >= 2 && (copy_out == nullptr || ldc >= N),
-             "gemm_pair_tc_resadd: bad sizes ldr=%d ldc=%d", ldr, ldc);
+  MS_REQUIRE(residual != nullptr && stats_out != nullptr && ldr >= N && ldr % 4 == 0 && (uintptr_t)residual % 16 == 0 && sm_count >= 2 &&
+                 (copy_out == nullptr || (ldc >= N && ldc % 4 == 0 && (uintptr_t)copy_out % 8 == 0)),
+             "gemm_pair_tc_resadd: bad sizes ldr=%d ldc=%d (multiples of 4, aligned rows)", ldr, ldc);
   const bool wide = pr_wide(M, N, sm_count);
   CUtensorMap mx, mw;
   if (int rc = pr_maps(&mx, &mw, x, ldx, w, M, N, K, wide ? 128 : 64)) return rc;
-  PrExtra ex = {nullptr, 0, 0.f, 0, residual, ldr, stats_out, (N + 15) / 16, (__nv_bfloat16*)copy_out, ldc};
+  PrExtra ex = {nullptr, 0, 0.f, 0, residual, ldr, stats_out, ms_gemm_pair_tc_stats_blocks(M, N, sm_count), (__nv_bfloat16*)copy_out, ldc};
   return wide ? pr_launch<256, PR_EPI_RESADD, 0>(mx, mw, nullptr, 0, M, N, K, ex, sm_count, stream)
               : pr_launch<128, PR_EPI_RESADD, 0>(mx, mw, nullptr, 0, M, N, K, ex, sm_count, stream);
 }

@@ -683,15 +683,21 @@ def gemm_pair_tc_silu_mul(x, w_gate_up, out, stats=None, stats_blocks=0, eps=0.0
     return out
 
 
+def gemm_pair_tc_stats_blocks(m: int, n: int) -> int:
+    """How many sums of squares per row `gemm_pair_tc_resadd` leaves for a residual of [m, n] (one per tile of columns)."""
+    return int(lib().ms_gemm_pair_tc_stats_blocks(int(m), int(n), sm_count()))
+
+
 def gemm_pair_tc_resadd(x, w, residual, stats_out, copy_out=None):
     """residual[M, N] += x[M, K] . w[N, K]^T in place (float32), the sums of squares of the new residual per row and
-    block of 16 columns (as gemm_small_m_resadd leaves them), and optionally its bfloat16 copy; any number of rows."""
+    tile of columns (`gemm_pair_tc_stats_blocks` of them a row; a consumer adds up all of a row's), and optionally its
+    bfloat16 copy; any number of rows."""
     m, k = x.shape
     n = w.shape[0]
     _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and residual.dtype == torch.float32, "gemm_pair_tc_resadd: bad dtypes")
     _need(w.is_contiguous() and w.shape[1] == k and x.stride(1) == 1 and residual.stride(1) == 1, "gemm_pair_tc_resadd: bad layout")
     _need(tuple(residual.shape) == (m, n), "gemm_pair_tc_resadd: the residual must be [rows, N]")
-    _need(stats_out.dtype == torch.float32 and stats_out.is_contiguous() and stats_out.numel() >= m * gemm_small_m_stats_blocks(n),
+    _need(stats_out.dtype == torch.float32 and stats_out.is_contiguous() and stats_out.numel() >= m * gemm_pair_tc_stats_blocks(m, n),
           "gemm_pair_tc_resadd: bad stats buffer")
     _need(copy_out is None or (copy_out.dtype == torch.bfloat16 and tuple(copy_out.shape) == (m, n) and copy_out.stride(1) == 1),
           "gemm_pair_tc_resadd: the copy must be bfloat16 [rows, N]")

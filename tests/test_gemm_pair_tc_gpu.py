@@ -47,7 +47,7 @@ def test_gemm_pair_tc_silu_mul(m, i, k):
     assert np.abs(N(out) - want).max() <= 2.0 ** -8 * max(1.0, np.abs(want).max()) + 1e-4
 
 
-@pytest.mark.parametrize("m,n,k", [(300, 200, 72), (129, 136, 264), (512, 896, 4864), (1000, 1536, 512), (3, 20, 16)])
+@pytest.mark.parametrize("m,n,k", [(300, 200, 72), (129, 136, 264), (512, 896, 4864), (1000, 1536, 512), (3, 24, 16)])
 def test_gemm_pair_tc_resadd(m, n, k):
     import torch
     from machserve_b200 import ops
@@ -57,14 +57,22 @@ def test_gemm_pair_tc_resadd(m, n, k):
     want = res0.astype(np.float64) + N(x) @ N(w).T
     scale = max(1.0, np.abs(want).max())
     res = T(res0)
-    nb = ops.gemm_small_m_stats_blocks(n)
+    nb = ops.gemm_pair_tc_stats_blocks(m, n)
     stats = torch.full((m, nb), -1.0, dtype=torch.float32, device=dev())
     copy = torch.full((m, n), 7.0, dtype=torch.bfloat16, device=dev())
     ops.gemm_pair_tc_resadd(x, w, res, stats, copy)
     assert ops.gemm_tc_status() == 0
     assert np.abs(N(res) - want).max() <= 2e-5 * scale
     assert np.abs(N(copy) - want).max() <= 2.0 ** -8 * scale
-    pad = np.zeros((m, nb * 16))
-    pad[:, :n] = N(res)
-    blocks = (pad.reshape(m, nb, 16) ** 2).sum(2)
-    assert np.abs(N(stats) - blocks).max() <= 1e-5 * max(1.0, blocks.max())
+    # the sums of squares: one per row and tile of columns, whatever the tile's width; together the row's
+    assert (N(stats) >= 0).all()
+    rows = (N(res) ** 2).sum(1)
+    assert np.abs(N(stats).sum(1) - rows).max() <= 1e-5 * max(1.0, rows.max())
+
+
+def test_gemm_pair_tc_refuses_widths_that_are_no_multiple_of_8():
+    import torch
+    from machserve_b200 import ops
+    x, w = torch.zeros((4, 16), dtype=torch.bfloat16, device=dev()), torch.zeros((20, 16), dtype=torch.bfloat16, device=dev())
+    with pytest.raises(ops.KernelError, match="multiples? of 8"):
+        ops.gemm_pair_tc(x, w, torch.zeros((4, 20), dtype=torch.bfloat16, device=dev()))
