@@ -81,6 +81,9 @@ class SwiGLU(FeedForward):
         if rt.dtype == torch.bfloat16 and ops.gemm_small_m_preferred(t, self.inter, self.hidden):
             # few rows: gate, up and the gating in one pass over the weights
             ops.gemm_small_m_silu_mul(x, self.w_gate_up[: self.inter], self.w_gate_up[self.inter :], h)
+        elif rt.dtype == torch.bfloat16 and ops.gemm_pair_tc_silu_preferred(t, self.inter, self.hidden):
+            # many rows of a wide model: the gating in the epilogue of this repository's tcgen05 product
+            ops.gemm_pair_tc_silu_mul(x, self.w_gate_up, h)
         else:
             gate_up = ws.get("ffn.gate_up", (t, 2 * self.inter), rt.dtype)
             ops.linear(x, self.w_gate_up, None, gate_up)
