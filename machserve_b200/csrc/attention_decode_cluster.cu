@@ -77,6 +77,30 @@ __device__ __noinline__ void dcl_load_round(__nv_bfloat16* kv_s, const __nv_bflo
   ms_cp_async_commit();
 }
 
+// A warp requests ITS part of a tile (KPW keys, the rows it will attend to itself) into the stage at `tile_s`: a warp
+// that copies what it reads needs no barrier of the block around its copies.  `page`: the page the tile lies in
+// (-1: none), `key0`: the tile's first key.  One group of copies (also when there is nothing to copy).
+template <int HD, int KPW>
+__device__ __forceinline__ void dcl_load_part(__nv_bfloat16* tile_s, const __nv_bfloat16* k_pages, const __nv_bfloat16* v_pages, int page,
+                                              int num_pages, int page_size, size_t page_elems, size_t head_off, int key0, int krow0,
+                                              int first_key, int last_key, bool any, int lane) {
+  constexpr int STRIDE = HD + 8, TILE_ELEMS = DCL_TILE * STRIDE, CHUNKS = HD / 8;
+  if (any) {
+    const bool page_ok = page >= 0 && page < num_pages;
+    const size_t off = (page_ok ? (size_t)page * page_elems + head_off + (size_t)(key0 % page_size) * HD : 0);
+#pragma unroll
+    for (int j = 0; j < KPW * CHUNKS / 32; ++j) {
+      const int idx = lane + 32 * j, r = krow0 + idx / CHUNKS, ch = idx % CHUNKS;
+      const int key = key0 + r;
+      const bool ok = page_ok && key >= first_key && key <= last_key;
+      __nv_bfloat16* dst = tile_s + r * STRIDE + ch * 8;
+      ms_cp_async16(dst, ok ? k_pages + off + (size_t)r * HD + ch * 8 : k_pages, ok);
+      ms_cp_async16(dst + TILE_ELEMS, ok ? v_pages + off + (size_t)r * HD + ch * 8 : v_pages, ok);
+    }
+  }
+  ms_cp_async_commit();
+}
+
 // KPW: keys a warp takes at a time: 64, a whole tile, or 32, half a tile.  DCL_WARPS: 4 or 8.  Four warps with a
 // tile each serve blocks with long runs of keys; four warps with half a tile each, blocks that can hold only two
 // tiles (many blocks on the GPU: more of them share an SM); eight warps with half a tile each, the few blocks of a
@@ -124,12 +148,27 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
 
   const int n_my = my_hi - my_lo + 1;
   // A run of keys that the stages hold at once is requested whole, before the wait.  A longer run goes through the
-  // stages in two halves: while the warps attend to the tiles of one half, the copies of the next round fill the other.
-  const bool pipelined = n_my > stages && stages >= 2;
-  const int per_round = pipelined ? stages / 2 : stages;
-  // the first round of tiles, without the current position's row
-  dcl_load_round<HD, DCL_THREADS>(kv_s, k_pages, v_pages, table, num_pages, page_size, page_elems, head_off, my_lo, min(per_round, max(n_my, 0)),
-                     first_key, pos, pos, tid);
+  // stages as a ring, a tile at a time: while the warps attend to one tile (a part of it each), the copies of the
+  // `stages - 1` tiles after it are on their way.  Every warp copies the part of a tile that it attends to itself, so
+  // the warps go through the ring each at its own pace, without a barrier of the block.  That needs the warps to share
+  // a tile evenly and tiles that lie inside pages; other shapes take the run in rounds of `stages` tiles.
+  const bool ring = n_my > stages && n_my <= 64 && stages >= 2 && KPW * DCL_WARPS == DCL_TILE && page_size % DCL_TILE == 0;
+  const int fill = min(stages, max(n_my, 0));  // tiles requested before the wait, without the current position's row
+  // ring: lane l knows the pages of the block's tiles l and 32 + l, so that no copy has to wait for a look-up
+  int ring_page[2] = {-1, -1};
+  if (ring) {
+    const int tiles_per_page = page_size / DCL_TILE;
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+      if (32 * h + lane < n_my) ring_page[h] = table[(my_lo + 32 * h + lane) / tiles_per_page];
+#pragma unroll 1
+    for (int s = 0; s < fill; ++s)  // a group of copies per tile
+      dcl_load_part<HD, KPW>(kv_s + (size_t)s * 2 * TILE_ELEMS, k_pages, v_pages, __shfl_sync(0xffffffffu, ring_page[0], s), num_pages,
+                             page_size, page_elems, head_off, (my_lo + s) * DCL_TILE, warp * KPW, first_key, pos, true, lane);
+  } else {
+    dcl_load_round<HD, DCL_THREADS>(kv_s, k_pages, v_pages, table, num_pages, page_size, page_elems, head_off, my_lo, fill, first_key, pos,
+                                    pos, tid);
+  }
 
   ms_pdl_wait();
   MS_TIMELINE_WAITED();
@@ -155,7 +194,7 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
         const int page = table[pos / page_size];
         page_ok = page >= 0 && page < num_pages;
         cache_off = (size_t)(page_ok ? page : 0) * page_elems + head_off + (size_t)(pos % page_size) * HD;
-        if (ptile - my_lo < per_round)  // else the tile is copied from the cache in a later round, after a barrier
+        if (ptile - my_lo < fill)  // else the tile is copied from the cache later, after a barrier
           tile_row = kv_s + (size_t)(ptile - my_lo) * 2 * TILE_ELEMS + (pos - ptile * DCL_TILE) * STRIDE;
       }
       // heads 0 .. groups-1: the group's query heads; then (mine) the key head and the value head
@@ -221,7 +260,7 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
   }
   // the current position's own key and value, if its tile is in the first round
   {
-    if (!row_done && live && ptile >= my_lo && ptile <= my_hi && ptile - my_lo < per_round && tid < 2 * (HD / 8)) {
+    if (!row_done && live && ptile >= my_lo && ptile <= my_hi && ptile - my_lo < fill && tid < 2 * (HD / 8)) {
       const int which = tid / (HD / 8), ch = tid - which * (HD / 8);
       const int page = table[pos / page_size];
       const bool ok = page >= 0 && page < num_pages;
@@ -238,47 +277,52 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
   st.init();
   unsigned qa[HD / 16][4];
   const int lo[2] = {first_key, first_key}, hi[2] = {pos, pos};
-  // Rounds of up to `per_round` tiles; within a round warp w takes the parts w, w + DCL_WARPS, ... of the round's tiles.
-  if (pipelined) {
-    __syncthreads();  // the current position's key and value are in the cache before a later round is copied from it
-    dcl_load_round<HD, DCL_THREADS>(kv_s + (size_t)per_round * 2 * TILE_ELEMS, k_pages, v_pages, table, num_pages, page_size, page_elems,
-                                    head_off, my_lo + per_round, min(per_round, n_my - per_round), first_key, pos, -1, tid);
-  }
-#pragma unroll 1
-  for (int r0 = 0, round = 0; r0 < n_my; r0 += per_round, ++round) {
-    const int nr = min(per_round, n_my - r0);
-    __nv_bfloat16* buf = kv_s + (pipelined && (round & 1) ? (size_t)per_round * 2 * TILE_ELEMS : 0);
-    if (!pipelined && r0 > 0) {
-      __syncthreads();  // every warp is done with the stages
-      dcl_load_round<HD, DCL_THREADS>(kv_s, k_pages, v_pages, table, num_pages, page_size, page_elems, head_off, my_lo + r0, nr, first_key,
-                         pos, -1, tid);
-    }
-    if (pipelined) {
-      ms_cp_async_wait<1>();  // this round's copies have landed; the next round's may still be on their way
-    } else {
-      ms_cp_async_wait<0>();
-    }
-    __syncthreads();
-    if (r0 == 0) {
-      const int mat = lane >> 3, within = lane & 7;
+  const int mat = lane >> 3, within = lane & 7;
+  if (ring) {
+    __syncthreads();  // the query rows are in place, and the current position's key and value are in the cache
 #pragma unroll
-      for (int ks = 0; ks < HD / 16; ++ks)
-        ms_ldmatrix_x4(qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3],
-                       q_s + (within + 8 * (mat & 1)) * STRIDE + ks * 16 + 8 * (mat >> 1));
-    }
-    constexpr int PARTS = DCL_TILE / KPW;  // parts of a tile
+    for (int ks = 0; ks < HD / 16; ++ks)
+      ms_ldmatrix_x4(qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], q_s + (within + 8 * (mat & 1)) * STRIDE + ks * 16 + 8 * (mat >> 1));
+    // a thread's groups of copies so far: `stages` tiles, the current row's (empty here), then one per tile done (the
+    // last ones empty): its part of tile i has landed when at most stages - 1 groups are still on their way
 #pragma unroll 1
-    for (int sl = warp; sl < nr * PARTS; sl += DCL_WARPS) {
-      const int i = sl / PARTS, krow = (sl % PARTS) * KPW;
-      const __nv_bfloat16* ks = buf + (size_t)i * 2 * TILE_ELEMS;
-      ms_attend_keys<HD, KPW / 16, true>(st, qa, ks, ks + TILE_ELEMS, krow, (my_lo + r0 + i) * DCL_TILE + krow, lo, hi, first_key,
+    for (int i = 0; i < n_my; ++i) {
+      ms_cp_async_wait_dynamic(stages - 1);
+      __syncwarp();
+      __nv_bfloat16* buf = kv_s + (size_t)(i % stages) * 2 * TILE_ELEMS;
+      ms_attend_keys<HD, KPW / 16, true>(st, qa, buf, buf + TILE_ELEMS, warp * KPW, (my_lo + i) * DCL_TILE + warp * KPW, lo, hi, first_key,
                                          pos, scale_log2, lane);
+      __syncwarp();  // the warp is done with its part of the stage
+      const int nx = i + stages;
+      const int page = __shfl_sync(0xffffffffu, nx < 32 ? ring_page[0] : ring_page[1], nx & 31);
+      dcl_load_part<HD, KPW>(buf, k_pages, v_pages, page, num_pages, page_size, page_elems, head_off, (my_lo + nx) * DCL_TILE, warp * KPW,
+                             first_key, pos, nx < n_my, lane);
     }
-    if (pipelined) {
-      __syncthreads();  // every warp is done with this half: the round after the next goes there (an empty
-      const int nx = r0 + 2 * per_round;  // request keeps the count of copy groups in step)
-      dcl_load_round<HD, DCL_THREADS>(buf, k_pages, v_pages, table, num_pages, page_size, page_elems, head_off, my_lo + nx,
-                                      max(0, min(per_round, n_my - nx)), first_key, pos, -1, tid);
+  } else {
+    // rounds of up to `stages` tiles; within a round warp w takes the parts w, w + DCL_WARPS, ... of the round's tiles
+#pragma unroll 1
+    for (int r0 = 0; r0 < n_my; r0 += stages) {
+      const int nr = min(stages, n_my - r0);
+      if (r0 > 0) {
+        __syncthreads();  // every warp is done with the stages
+        dcl_load_round<HD, DCL_THREADS>(kv_s, k_pages, v_pages, table, num_pages, page_size, page_elems, head_off, my_lo + r0, nr, first_key,
+                                        pos, -1, tid);
+      }
+      ms_cp_async_wait<0>();
+      __syncthreads();
+      if (r0 == 0) {
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks)
+          ms_ldmatrix_x4(qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], q_s + (within + 8 * (mat & 1)) * STRIDE + ks * 16 + 8 * (mat >> 1));
+      }
+      constexpr int PARTS = DCL_TILE / KPW;  // parts of a tile
+#pragma unroll 1
+      for (int sl = warp; sl < nr * PARTS; sl += DCL_WARPS) {
+        const int i = sl / PARTS, krow = (sl % PARTS) * KPW;
+        const __nv_bfloat16* ks = kv_s + (size_t)i * 2 * TILE_ELEMS;
+        ms_attend_keys<HD, KPW / 16, true>(st, qa, ks, ks + TILE_ELEMS, krow, (my_lo + r0 + i) * DCL_TILE + krow, lo, hi, first_key,
+                                           pos, scale_log2, lane);
+      }
     }
   }
   ms_cp_async_wait<0>();
@@ -450,12 +494,10 @@ static int launch_decode_cluster(const void* q, DclRaw raw, const void* k_pages,
 
 MS_TIMELINE_SETTER(ms_timeline_set_attention_decode_cluster)
 
-// The most tiles a block can hold at once for a head size: about 100 KB of shared memory, which leaves room on the
-// SM for the blocks of the kernels that follow (they request their weights early); 144 KB for wide heads, so that
-// a block still holds four tiles.
+// The most tiles a block can hold at once for a head size (about 100 KB of shared memory, which leaves room on the SM
+// for the blocks of the kernels that follow: they request their weights early).
 MS_API int ms_attention_decode_cluster_max_stages(int hd) {
-  const size_t room = hd > 64 ? 144 * 1024 : 100 * 1024;
-  int s = (int)(room / ((size_t)2 * DCL_TILE * (hd + 8) * sizeof(__nv_bfloat16)));
+  int s = (int)((100 * 1024) / ((size_t)2 * DCL_TILE * (hd + 8) * sizeof(__nv_bfloat16)));
   return s < 1 ? 1 : (s > 8 ? 8 : s);
 }
 

@@ -215,12 +215,13 @@ class Attention(Mixer):
         return self.attend(ctx, self.encode_store(ctx, qkv, cache, store), cache, out)
 
     def _single_launch(self, units: int, tiles: int):
-        """(splits, stages, warps) for `units` (row, kv head) pairs whose longest run of keys has `tiles` tiles of 64.
-        What the measurements on B200 (head sizes 64 and 128, 8 to 64 rows, 1,000 to 2,048 keys) come to: all blocks
-        of the launch are resident at once (a second wave costs more than fewer, longer blocks), as many splits as
-        that allows up to three and a half blocks per SM, never more blocks than half the tiles.  A block holds its
-        whole run of tiles when that fits (all of it is requested before the wait for the preceding kernel), else it
-        goes through the run with four or two tiles at a time, or with one when the run is short."""
+        """(splits, stages, warps, keys per warp) for `units` (row, kv head) pairs whose longest run of keys has `tiles`
+        tiles of 64.  What the measurements on B200 (head sizes 64 and 128, 8 to 64 rows, 1,000 to 2,048 keys) come to:
+        all blocks of the launch are resident at once (a second wave costs more than fewer, longer blocks), as many
+        splits as that allows up to three and a half blocks per SM, never more blocks than half the tiles.  A block
+        holds its whole run of tiles when that fits (all of it is requested before the wait for the preceding
+        kernel); else it goes through the run with a ring of four or two stages (more blocks on an SM hide the
+        latency of a row's chain of steps better than a deeper ring does), or, when the run is short, a tile at a time."""
         key = (units, tiles)
         hit = self._launch_cache.get(key)
         if hit is not None:
@@ -234,16 +235,18 @@ class Attention(Mixer):
             ring = [n for n in (4, 2, 1) if n < per and n <= self.max_stages and (n <= 2 or hd <= 64) and (n > 1 or per <= 4)]
             for stages in ([per] if per <= self.max_stages else []) + ring:
                 if blocks <= sm * ops.attention_decode_cluster_blocks_per_sm(hd, stages):
-                    choice = (splits, stages)
+                    choice = (splits, stages, per)
                     break
             if choice:
                 break
-        splits, stages = choice or (1, min(2, self.max_stages, tiles))
+        splits, stages, per = choice or (1, min(2, self.max_stages, tiles), tiles)
         blocks = splits * units
-        # the few blocks of a small batch (one per SM at most): eight warps, half a tile each
-        warps = 8 if stages >= 4 and blocks <= sm and hd <= 64 else 4
-        self._launch_cache[key] = (splits, stages, warps)
-        return splits, stages, warps
+        # the few blocks of a small batch (one per SM at most) that hold their whole runs: eight warps, half a tile each;
+        # a ring wants four warps with a quarter of a tile each
+        warps = 8 if stages >= 4 and stages >= per and blocks <= sm and hd <= 64 else 4
+        kpw = 16 if 2 <= stages < per else 0
+        self._launch_cache[key] = (splits, stages, warps, kpw)
+        return self._launch_cache[key]
 
     def _attend_single(self, ctx, q, cache, out, raw=None):
         """Rows that are alone in their sequences: a cluster of blocks per (row, kv head)."""
@@ -253,17 +256,18 @@ class Attention(Mixer):
         tiles = (work.shape[0] * self.CONTEXT_BUCKET + 63) // 64  # of the longest decoding context, by bucket
         if self.window:
             tiles = min(tiles, (self.window + 63) // 64 + 1)
-        splits, stages, warps = self._single_launch(t * self.hkv, tiles)
+        splits, stages, warps, kpw = self._single_launch(t * self.hkv, tiles)
         if raw is not None:
             qkv, store = raw
             return ops.attention_decode_cluster_rope(
                 qkv, self.bias, self.table, store, cache.k_pages, cache.v_pages, out, ctx.positions, ctx.slot_of_token,
-                table, self.hq, self.hkv, self.hd, self.window, self.scale, splits, stages, warps=warps,
+                table, self.hq, self.hkv, self.hd, self.window, self.scale, splits, stages, warps=warps, keys_per_warp=kpw,
             )
         return ops.attention_decode_cluster(
             q, cache.k_pages, cache.v_pages, out, ctx.positions, ctx.slot_of_token, table, self.hq, self.hkv,
             self.hd, self.window, self.scale, splits, stages,
             rows=None if work.sizes["tile_row0"] == 0 and t == q.shape[0] else work.lists["single_rows"], num_rows=t, warps=warps,
+            keys_per_warp=kpw,
         )
 
     def attend(self, ctx, q, cache, out):
