@@ -951,11 +951,14 @@ MS_API int ms_gemm_rows_tc_resadd(const void* x, int ldx, const void* w, float* 
 //              sums of squares that RESADD left: the RMS norm for a matrix with the norm's weight folded in
 //   SILU_MUL   block 0 holds BN/2 gate rows, block 1 the BN/2 up rows of the same outputs; out = silu(gate) * up
 //   RESADD     residual (float32) += acc in place; a bfloat16 copy of the new residual; its sums of squares
-//              per row and tile of columns (a consumer adds up all of a row's sums, however many there are)
+//              per row and half tile of columns (a consumer adds up all of a row's sums, however many there are)
 #define PR_BK 64
-#define PR_THREADS 192
+#define PR_THREADS 320  // a copying warp, an issuing warp, eight epilogue warps
 #define PR_MAX_STAGES 8
-#define PR_STAGE_BYTES_PER_WARP (32 * 144)  // where a warp's 32 rows x 32 columns change hands in the epilogue
+// where a warp's 32 rows x 32 columns change hands in the epilogue: rows of 144 bytes (float32) or of 80 (bfloat16)
+#define PR_EXCHANGE_BYTES(EPI) ((EPI) == PR_EPI_RESADD ? 32 * 144 : 32 * 80)
+// stages of the ring: what the exchange leaves of the shared memory
+#define PR_STAGES(BN, EPI) ((BN) == 256 ? ((EPI) == PR_EPI_RESADD ? 5 : 6) : ((EPI) == PR_EPI_RESADD ? 7 : 8))
 #define PR_PEER_MASK 0xFEFFFFFFu  // a shared::cluster address with this bit cleared is block 0's copy of the same place
 enum { PR_EPI_BF16 = 0, PR_EPI_SILU_MUL = 1, PR_EPI_RESADD = 2 };
 
@@ -1033,7 +1036,7 @@ gemm_pair_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     __nv_bfloat16* __restrict__ out, int ldo, int M, int N, int K, int tiles_m, int num_tiles, PrExtra ex) {
   constexpr int HALF = BN / 2;                          // weight rows a block holds of a tile
   constexpr int STAGE_BYTES = (128 + HALF) * PR_BK * 2;  // per block
-  constexpr int STAGES = BN == 256 ? 6 : 8;
+  constexpr int STAGES = PR_STAGES(BN, EPI);
   constexpr int OUT_COLS = EPI == PR_EPI_SILU_MUL ? HALF : BN;  // output columns of a tile
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -1051,7 +1054,7 @@ gemm_pair_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     }
     for (int b = 0; b < 2; ++b) {
       tc_mbar_init(tc_smem(&sh->acc_full[b]), 1);     // each block's own
-      tc_mbar_init(tc_smem(&sh->acc_empty[b]), 256);  // block 0's: the epilogue threads of both blocks
+      tc_mbar_init(tc_smem(&sh->acc_empty[b]), 512);  // block 0's: the epilogue threads of both blocks
     }
     sh->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -1122,8 +1125,10 @@ gemm_pair_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     // of the block's half of the tile, 32 columns at a time, a row per thread; the values then change hands through
     // the warp's piece of shared memory so that a thread holds consecutive columns of few rows and global memory is
     // read and written in whole rows of the chunk (a row per thread would cost a transaction per thread and access).
+    // Eight warps: two for each group of 32 rows, one for the left half of the tile's columns and one for the right.
     const int group = warp & 3;
-    unsigned char* stage = reinterpret_cast<unsigned char*>(sh) + 1024 + (warp - 2) * PR_STAGE_BYTES_PER_WARP;
+    const int c_begin = warp >= 6 ? OUT_COLS / 2 : 0, c_end = c_begin + OUT_COLS / 2;
+    unsigned char* stage = reinterpret_cast<unsigned char*>(sh) + 1024 + (warp - 2) * PR_EXCHANGE_BYTES(EPI);
     int count = 0;
     bool ok = true;
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++count) {
@@ -1148,7 +1153,7 @@ gemm_pair_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           ss[i] = 0.f;
-          const int row = m_warp + 4 * i + rr, col = n0 + 4 * rq;
+          const int row = m_warp + 4 * i + rr, col = n0 + c_begin + 4 * rq;
           rold[i] = (row < M && col < N) ? *reinterpret_cast<const float4*>(ex.residual + (size_t)row * ex.ldr + col) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
       }
@@ -1158,7 +1163,7 @@ gemm_pair_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       tc_fence_after();
       const unsigned row_addr = tmem + buf * BN + ((unsigned)(group * 32) << 16);
 #pragma unroll 1
-      for (int c = 0; c < OUT_COLS; c += 32) {
+      for (int c = c_begin; c < c_end; c += 32) {
         float v[32];
         tc_ld32(row_addr + c, v);
         if (EPI == PR_EPI_SILU_MUL) {
@@ -1185,7 +1190,7 @@ gemm_pair_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             const int row = m_warp + 4 * i + rr, col = n + 4 * rq;
             const float4 acc = *reinterpret_cast<const float4*>(stage + (4 * i + rr) * 144 + 16 * rq);
             const float4 old = rold[i];
-            if (c + 32 < OUT_COLS)
+            if (c + 32 < c_end)
               rold[i] = (row < M && col + 32 < N) ? *reinterpret_cast<const float4*>(ex.residual + (size_t)row * ex.ldr + col + 32)
                                                   : make_float4(0.f, 0.f, 0.f, 0.f);
             if (row < M && col < N) {
@@ -1229,7 +1234,7 @@ gemm_pair_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           t += __shfl_xor_sync(0xffffffffu, t, 2);
           t += __shfl_xor_sync(0xffffffffu, t, 4);
           const int row = m_warp + 4 * i + rr;
-          if (rq == 0 && row < M) ex.stats_out[(size_t)row * ex.stats_out_nb + nt] = t;
+          if (rq == 0 && row < M) ex.stats_out[(size_t)row * ex.stats_out_nb + 2 * nt + (warp >= 6 ? 1 : 0)] = t;
         }
       }
       tc_fence_before();
@@ -1252,8 +1257,8 @@ gemm_pair_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 template <int BN, int EPI, int SCALE>
 static int pr_launch(const CUtensorMap& mx, const CUtensorMap& mw, void* out, int ldo, int M, int N, int K, const PrExtra& ex,
                      int sm_count, cudaStream_t stream) {
-  constexpr int STAGES = BN == 256 ? 6 : 8;
-  const size_t smem = (size_t)STAGES * (128 + BN / 2) * PR_BK * 2 + 1024 + 4 * PR_STAGE_BYTES_PER_WARP + 1024;
+  constexpr int STAGES = PR_STAGES(BN, EPI);
+  const size_t smem = (size_t)STAGES * (128 + BN / 2) * PR_BK * 2 + 1024 + 8 * PR_EXCHANGE_BYTES(EPI) + 1024;
   auto kern = gemm_pair_tc_kernel<BN, EPI, SCALE>;
   static bool configured = false;
   if (!configured) {
@@ -1284,11 +1289,12 @@ static int pr_launch(const CUtensorMap& mx, const CUtensorMap& mw, void* out, in
   return 0;
 }
 
-// Tiles of 256 columns when they give the pairs of SMs about as much to do as tiles of 128 would (the tensor core is fed
-// fully only by the wide ones).
+// Tiles of 256 or of 128 columns: by the rounds the pairs of SMs need for all tiles, times what a step of K costs with
+// that width (the tensor core is fed fully only by the wide tiles: a narrow one costs 0.72 of a wide one, not half).
 static bool pr_wide(int M, int N, int sm_count) {
-  const long long tm = (M + 255) / 256;
-  return tm * ((N + 255) / 256) >= (long long)(sm_count / 2) * 9 / 10;
+  const long long tm = (M + 255) / 256, pairs = sm_count / 2;
+  const long long wide = (tm * ((N + 255) / 256) + pairs - 1) / pairs, narrow = (tm * ((N + 127) / 128) + pairs - 1) / pairs;
+  return wide * 100 <= narrow * 72;
 }
 
 static int pr_maps(CUtensorMap* mx, CUtensorMap* mw, const void* x, int ldx, const void* w, int M, int w_rows, int K, int w_box) {
@@ -1331,8 +1337,8 @@ MS_API int ms_gemm_pair_tc_silu_mul(const void* x, int ldx, const void* w_gate_u
   return pr_launch<256, PR_EPI_SILU_MUL, 0>(mx, mw, out, ldo, M, I, K, ex, sm_count, stream);
 }
 
-// How many sums of squares a row of ms_gemm_pair_tc_resadd's stats_out has (one per tile of columns).
-MS_API int ms_gemm_pair_tc_stats_blocks(int M, int N, int sm_count) { return pr_wide(M, N, sm_count) ? (N + 255) / 256 : (N + 127) / 128; }
+// How many sums of squares a row of ms_gemm_pair_tc_resadd's stats_out has (two per tile of columns: one per epilogue warp).
+MS_API int ms_gemm_pair_tc_stats_blocks(int M, int N, int sm_count) { return 2 * (pr_wide(M, N, sm_count) ? (N + 255) / 256 : (N + 127) / 128); }
 
 // residual[M, N] (float32) += x[M, K] . w[N, K]^T in place; stats_out[m][b] = the sum of squares of the new
 // residual's row m over its b-th tile of columns (ms_gemm_pair_tc_stats_blocks of them a row); copy_out (or null):

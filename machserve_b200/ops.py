@@ -669,13 +669,14 @@ def gemm_pair_tc(x, w, out, stats=None, stats_blocks=0, eps=0.0):
 
 
 # From where the gated product with the gating in its epilogue beats the library's product followed by the gating
-# kernel (measured on B200: at K = 3,584 by 7 % at 2,048 rows and by 16 % at 4,152; at K = 1,536 it does not).
+# kernel (measured on B200 at K = 896, 1,536, 2,048 and 3,584, 256 to 4,152 rows: from 1,024 rows on by 6 to 17 %,
+# at K = 896 only from 2,048 rows on; below 1,024 rows the library wins).
 PAIR_TC_SILU_MIN_ROWS = 1024
-PAIR_TC_SILU_MIN_K = 2048
+PAIR_TC_SILU_MIN_ROWS_NARROW = 2048  # for K below 1,024
 
 
 def gemm_pair_tc_silu_preferred(m: int, i: int, k: int) -> bool:
-    return m >= PAIR_TC_SILU_MIN_ROWS and k >= PAIR_TC_SILU_MIN_K and i % 8 == 0 and k % 8 == 0
+    return m >= (PAIR_TC_SILU_MIN_ROWS if k >= 1024 else PAIR_TC_SILU_MIN_ROWS_NARROW) and i % 8 == 0 and k % 8 == 0
 
 
 def gemm_pair_tc_silu_mul(x, w_gate_up, out, stats=None, stats_blocks=0, eps=0.0):
