@@ -201,6 +201,21 @@ def time_gemm_pair_tc(torch, ops, a, pk) -> int:
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / (2 * reps) * 1000
 
+    if a.profile:  # one launch each of the gated product, the same product plain and the library's, for a profiler
+        for _ in range(3):
+            ops.gemm_pair_tc_silu_mul(x, w_gu, o_i)
+            ops.gemm_pair_tc(x, w_gu, o_gu)
+            torch.mm(x, w_gu.T, out=o_gu)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        ops.gemm_pair_tc_silu_mul(x, w_gu, o_i)
+        ops.gemm_pair_tc(x, w_gu, o_gu)
+        torch.mm(x, w_gu.T, out=o_gu)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        assert ops.gemm_tc_status() == 0
+        print(json.dumps({"kernel": "gemm_pair_tc", "shape": a.shape, "rows": m, "profiled": ["gate_up_silu_mul", "gate_up_plain", "library"]}))
+        return 0
     out = {}
     for name, own, lib, flops in (
         ("qkv_norm_folded", lambda: ops.gemm_pair_tc(x, w_qkv, o_qkv, stats, nb, 1e-6), lambda: torch.mm(x, w_qkv.T, out=o_qkv), 2 * m * h * qkv),
