@@ -152,19 +152,27 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
   // `stages - 1` tiles after it are on their way.  Every warp copies the part of a tile that it attends to itself, so
   // the warps go through the ring each at its own pace, without a barrier of the block.  That needs the warps to share
   // a tile evenly and tiles that lie inside pages; other shapes take the run in rounds of `stages` tiles.
-  const bool ring = n_my > stages && n_my <= 64 && stages >= 2 && KPW * DCL_WARPS == DCL_TILE && page_size % DCL_TILE == 0;
+  // (the warps of a block take the keys of G tiles between them: G = 1 with four warps of 16 keys, 2 with eight)
+  constexpr int G = KPW * DCL_WARPS / DCL_TILE;
+  constexpr bool RINGS = G >= 1 && KPW * DCL_WARPS == G * DCL_TILE;
+  const int slots = RINGS ? stages / (G > 0 ? G : 1) : 0;  // places of the ring, of G tiles each
+  const bool ring = RINGS && n_my > stages && n_my <= 64 && slots >= 2 && slots * G == stages && page_size % DCL_TILE == 0;
   const int fill = min(stages, max(n_my, 0));  // tiles requested before the wait, without the current position's row
-  // ring: lane l knows the pages of the block's tiles l and 32 + l, so that no copy has to wait for a look-up
+  // ring: lane l knows the pages of the block's tiles l and 32 + l, so that no copy has to wait for a look-up; a warp's
+  // part of a place of the ring is the keys krow .. krow + KPW - 1 of the place's tile wt
   int ring_page[2] = {-1, -1};
+  const int wt = warp * KPW / DCL_TILE, krow = warp * KPW % DCL_TILE;
   if (ring) {
     const int tiles_per_page = page_size / DCL_TILE;
 #pragma unroll
     for (int h = 0; h < 2; ++h)
       if (32 * h + lane < n_my) ring_page[h] = table[(my_lo + 32 * h + lane) / tiles_per_page];
 #pragma unroll 1
-    for (int s = 0; s < fill; ++s)  // a group of copies per tile
-      dcl_load_part<HD, KPW>(kv_s + (size_t)s * 2 * TILE_ELEMS, k_pages, v_pages, __shfl_sync(0xffffffffu, ring_page[0], s), num_pages,
-                             page_size, page_elems, head_off, (my_lo + s) * DCL_TILE, warp * KPW, first_key, pos, true, lane);
+    for (int s = 0; s < slots; ++s) {  // a group of copies per place
+      const int t = s * G + wt;
+      dcl_load_part<HD, KPW>(kv_s + (size_t)t * 2 * TILE_ELEMS, k_pages, v_pages, __shfl_sync(0xffffffffu, ring_page[0], t & 31), num_pages,
+                             page_size, page_elems, head_off, (my_lo + t) * DCL_TILE, krow, first_key, pos, t < n_my, lane);
+    }
   } else {
     dcl_load_round<HD, DCL_THREADS>(kv_s, k_pages, v_pages, table, num_pages, page_size, page_elems, head_off, my_lo, fill, first_key, pos,
                                     pos, tid);
@@ -283,20 +291,23 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
 #pragma unroll
     for (int ks = 0; ks < HD / 16; ++ks)
       ms_ldmatrix_x4(qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], q_s + (within + 8 * (mat & 1)) * STRIDE + ks * 16 + 8 * (mat >> 1));
-    // a thread's groups of copies so far: `stages` tiles, the current row's (empty here), then one per tile done (the
-    // last ones empty): its part of tile i has landed when at most stages - 1 groups are still on their way
+    // a thread's groups of copies so far: one per place, the current row's (empty here), then one per turn done (the
+    // last ones empty): its part of turn i has landed when at most slots - 1 groups are still on their way
+    const int turns = (n_my + G - 1) / G;
 #pragma unroll 1
-    for (int i = 0; i < n_my; ++i) {
-      ms_cp_async_wait_dynamic(stages - 1);
+    for (int i = 0; i < turns; ++i) {
+      ms_cp_async_wait_dynamic(slots - 1);
       __syncwarp();
-      __nv_bfloat16* buf = kv_s + (size_t)(i % stages) * 2 * TILE_ELEMS;
-      ms_attend_keys<HD, KPW / 16, true>(st, qa, buf, buf + TILE_ELEMS, warp * KPW, (my_lo + i) * DCL_TILE + warp * KPW, lo, hi, first_key,
-                                         pos, scale_log2, lane);
-      __syncwarp();  // the warp is done with its part of the stage
-      const int nx = i + stages;
-      const int page = __shfl_sync(0xffffffffu, nx < 32 ? ring_page[0] : ring_page[1], nx & 31);
-      dcl_load_part<HD, KPW>(buf, k_pages, v_pages, page, num_pages, page_size, page_elems, head_off, (my_lo + nx) * DCL_TILE, warp * KPW,
-                             first_key, pos, nx < n_my, lane);
+      const int t = i * G + wt;
+      __nv_bfloat16* buf = kv_s + (size_t)((i % slots) * G + wt) * 2 * TILE_ELEMS;
+      if (t < n_my)
+        ms_attend_keys<HD, KPW / 16, true>(st, qa, buf, buf + TILE_ELEMS, krow, (my_lo + t) * DCL_TILE + krow, lo, hi, first_key, pos,
+                                           scale_log2, lane);
+      __syncwarp();  // the warp is done with its part of the place
+      const int tn = (i + slots) * G + wt;
+      const int page = __shfl_sync(0xffffffffu, tn < 32 ? ring_page[0] : ring_page[1], tn & 31);
+      dcl_load_part<HD, KPW>(buf, k_pages, v_pages, page, num_pages, page_size, page_elems, head_off, (my_lo + tn) * DCL_TILE, krow,
+                             first_key, pos, tn < n_my, lane);
     }
   } else {
     // rounds of up to `stages` tiles; within a round warp w takes the parts w, w + DCL_WARPS, ... of the round's tiles
@@ -485,6 +496,8 @@ static int launch_decode_cluster(const void* q, DclRaw raw, const void* k_pages,
                                                         window, scale, num_splits, stages, stream)
   // few tiles a round, or wide heads (a long chain of steps per key): smaller parts keep every warp busy
   if (kpw == 0) kpw = warps == 8 ? 32 : HD > 64 ? 16 : stages <= 4 ? 32 : 64;
+  if (warps == 8 && kpw == 64) kpw = 32;
+  if (warps == 8 && kpw == 16) MS_DCL_LAUNCH(16, 8);
   if (warps == 8) MS_DCL_LAUNCH(32, 8);
   if (kpw == 16) MS_DCL_LAUNCH(16, 4);
   if (kpw == 32) MS_DCL_LAUNCH(32, 4);
@@ -552,7 +565,7 @@ static int decode_cluster_dispatch(const void* q, const DclRaw* raw, void* k_pag
 
 // As ms_attention_decode, without scratch memory.  num_splits: 1, 2, 4 or 8 (the cluster size).
 // stages: tiles of 64 keys a block holds at once, 1 .. ms_attention_decode_cluster_max_stages(hd).
-// warps: 4, or 8 (half a tile per warp: for the few blocks of a small batch).  keys_per_warp: the part of a tile a
+// warps: 4, or 8 (for the few blocks of a small batch: half a tile per warp, or a quarter when the run goes through a ring).  keys_per_warp: the part of a tile a
 // warp takes at a time with four warps, 16, 32 or 64; 0 chooses by the number of stages.
 MS_API int ms_attention_decode_cluster(const void* q, const void* k_pages, const void* v_pages, void* out,
                                        const int* rows, const int* positions, const int* slot_of_token,

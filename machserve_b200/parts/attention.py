@@ -241,10 +241,12 @@ class Attention(Mixer):
                 break
         splits, stages, per = choice or (1, min(2, self.max_stages, tiles), tiles)
         blocks = splits * units
-        # the few blocks of a small batch (one per SM at most) that hold their whole runs: eight warps, half a tile each;
-        # a ring wants four warps with a quarter of a tile each
-        warps = 8 if stages >= 4 and stages >= per and blocks <= sm and hd <= 64 else 4
-        kpw = 16 if 2 <= stages < per else 0
+        # the few blocks of a small batch (one per SM at most): eight warps, with half a tile each when the block holds its
+        # whole run, with a quarter each when it goes through a ring (of two places of two tiles); else four warps, and
+        # a quarter of a tile each in a ring
+        ring = 2 <= stages < per
+        warps = 8 if stages >= 4 and blocks <= sm and hd <= 64 else 4
+        kpw = 16 if ring else 0
         self._launch_cache[key] = (splits, stages, warps, kpw)
         return self._launch_cache[key]
 

@@ -311,7 +311,7 @@ def test_attention_decode(lens, hq, hkv, hd, page, window, splits):
 
 @pytest.mark.parametrize("lens,hq,hkv,hd,page,window", ATT_CASES)
 @pytest.mark.parametrize("splits,stages,warps,kpw", [(1, 1, 4, 0), (2, 8, 4, 0), (4, 2, 4, 0), (8, 1, 4, 0), (8, 8, 4, 0), (1, 4, 8, 0), (2, 8, 8, 0),
-                                                     (8, 5, 8, 0), (2, 2, 4, 16), (4, 1, 4, 32), (1, 3, 4, 64), (8, 4, 4, 16)])
+                                                     (8, 5, 8, 0), (2, 2, 4, 16), (4, 1, 4, 32), (1, 3, 4, 64), (8, 4, 4, 16), (2, 4, 8, 16), (1, 8, 4, 64), (1, 2, 4, 16)])
 def test_attention_decode_cluster(lens, hq, hkv, hd, page, window, splits, stages, warps, kpw):
     """The cluster variant: splits merged in shared memory, several tiles in flight, the current row copied late;
     four warps with a tile, half or a quarter of a tile each (`kpw`; 0: the kernel's own rule), and eight warps with
