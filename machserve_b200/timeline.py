@@ -27,7 +27,7 @@ from collections import defaultdict
 from typing import Dict, List
 
 # the files whose kernels carry hooks: each has a setter `ms_timeline_set_<unit>` in the timeline build
-UNITS = ("gemm_small_m", "attention_decode_cluster")
+UNITS = ("gemm_small_m", "attention_decode_cluster", "attention_decode_cluster_rope")
 # kernel ids as the hooks give them: 100 + 10 * epilogue + row scaling for the products, 200 for the attention
 NAMES = {100: "product -> bfloat16", 101: "product / rms -> bfloat16", 110: "product -> float32", 111: "product / rms -> float32",
          120: "gate/up, SiLU-mul", 121: "gate/up / rms, SiLU-mul", 130: "product + residual, row sums", 200: "decoding attention"}
