@@ -251,13 +251,13 @@ def time_attention_prefill(torch, ops, a, pk) -> int:
         t0 = torch.arange(0, n, 128, dtype=torch.int32, device=dev)
         tn = torch.full_like(t0, 128)
         tiles = t0.numel()
-        splits, alone = ops.attention_prefill_tc_plan(tiles, hq, hkv, hd, n, tiles * (tiles + 1) // 2)  # the engine's own choice
+        splits, alone, run_tiles = ops.attention_prefill_tc_plan(tiles, hq, hkv, hd, n, tiles * (tiles + 1) // 2)  # the engine's own choice
         words = ops.attention_prefill_tc_scratch_words(t0.numel(), hq, hd, splits)
         scratch = torch.zeros(words, dtype=torch.float32, device=dev) if words else None
         counters = torch.zeros(t0.numel() * hq, dtype=torch.int32, device=dev) if words else None
         def run():
             ops.attention_prefill_tc(q, kp, vp, out, t0, tn, t0.numel(), pos, slot, table, hq, hkv, hd, None, hd ** -0.5,
-                                     splits, scratch, counters, alone=alone)
+                                     splits, scratch, counters, alone=alone, run_tiles=run_tiles)
         for _ in range(max(a.warmup, 3)):
             run()
         torch.cuda.synchronize()
@@ -277,7 +277,7 @@ def time_attention_prefill(torch, ops, a, pk) -> int:
         us = e0.elapsed_time(e1) / (10 * reps) * 1000
         flops = 4 * hq * hd * n * (n + 1) / 2
         res[str(n)] = {"us": round(us, 1), "tflops": round(flops / us / 1e6, 1), "frac": round(flops / us / 1e6 / pk["bf16_tflops"], 3),
-                       "key_splits": splits, "heads_per_block": 1 if alone or hd == 64 else 2}
+                       "key_splits": splits, "key_tiles_a_run": run_tiles, "heads_per_block": 1 if alone or hd == 64 else 2}
     assert ops.gemm_tc_status() == 0
     print(json.dumps({"kernel": "attention_prefill_tc", "heads": hq, "kv_heads": hkv, "head_dim": hd, "page_size": page,
                       "dtype": "bf16", "tokens": res, "peaks": pk["source"]}))

@@ -321,7 +321,7 @@ attention_prefill_tc_single_kernel(const __grid_constant__ CUtensorMap map_q, co
                             const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
                             const int* __restrict__ positions, const int* __restrict__ slot_of_token,
                             const int* __restrict__ block_table, int max_pages, int num_pages, int hq, int hkv,
-                            int page_size, int window, float scale_log2, int num_runs, float* __restrict__ scratch,
+                            int page_size, int window, float scale_log2, int num_runs, int run_tiles, float* __restrict__ scratch,
                             int* __restrict__ counters) {
   constexpr int PANELS = HD / 64;          // 64-column panels of Q, K and V
   constexpr int PANEL_BYTES = 128 * 128;   // 128 rows of 128 bytes
@@ -347,8 +347,10 @@ attention_prefill_tc_single_kernel(const __grid_constant__ CUtensorMap map_q, co
   const int first_key = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
   const int item_lo = first_key / ATC_KEYS, tile_hi = pos_last / ATC_KEYS;
   const int item_tiles = (slot >= 0 && nrows > 0) ? tile_hi - item_lo + 1 : 0;
-  // the item's key tiles in `num_runs` runs of equal length; blocks past the last run have nothing to do
-  const int chunk = (item_tiles + nruns - 1) / nruns;
+  // the item's key tiles in runs of equal length for different blocks: `num_runs` of them, or (run_tiles > 0) as many as
+  // keep a run at `run_tiles` tiles at most, so that only long items are cut; blocks past the last run have nothing to do
+  const int want = run_tiles > 0 ? min(nruns, max(1, (item_tiles + run_tiles - 1) / run_tiles)) : nruns;
+  const int chunk = (item_tiles + want - 1) / want;
   const int nsplit = chunk > 0 ? (item_tiles + chunk - 1) / chunk : 1;
   const int split = blockIdx.y % nruns;
   const bool active = split < nsplit;
@@ -356,7 +358,12 @@ attention_prefill_tc_single_kernel(const __grid_constant__ CUtensorMap map_q, co
   const int ntiles = (active && chunk > 0) ? min(chunk, item_tiles - split * chunk) : 0;
   const int* table = block_table + (size_t)(slot >= 0 ? slot : 0) * max_pages;
 
-  if (tid == 0) {
+  // the copying thread sets the barriers up and sends for the query tile at once (nothing else lies there), while the
+  // others clear the stages and tensor memory is taken
+  if (warp == 4 && lane == 0) {
+    asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_q) : "memory");
+    asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_k) : "memory");
+    asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_v) : "memory");
     atc_mbar_init(atc_smem(&sh->q_full), 1);
     atc_mbar_init(atc_smem(&sh->k_full), 1);
     atc_mbar_init(atc_smem(&sh->k_empty), 1);
@@ -371,6 +378,10 @@ attention_prefill_tc_single_kernel(const __grid_constant__ CUtensorMap map_q, co
     sh->abort_flag = 0;
     sh->group_bad = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    if (ntiles > 0) {
+      atc_mbar_expect_tx(atc_smem(&sh->q_full), KV_BYTES);
+      for (int p = 0; p < PANELS; ++p) atc_tma_2d(atc_smem(q_s + p * PANEL_BYTES), &map_q, h * HD + p * 64, row0, atc_smem(&sh->q_full));
+    }
   }
   // the key and value stages start as zeros: rows that no page holds are never copied, and what multiplies a
   // probability of zero must be finite
@@ -389,11 +400,7 @@ attention_prefill_tc_single_kernel(const __grid_constant__ CUtensorMap map_q, co
   const unsigned tmem_p = tmem + 192;                 // 64 columns of packed bfloat16 P
 
   if (warp == 4 && lane == 0) {
-    // ------------------------------------------------------------------ producer
-    if (ntiles > 0) {
-      atc_mbar_expect_tx(atc_smem(&sh->q_full), KV_BYTES);
-      for (int p = 0; p < PANELS; ++p) atc_tma_2d(atc_smem(q_s + p * PANEL_BYTES), &map_q, h * HD + p * 64, row0, atc_smem(&sh->q_full));
-    }
+    // ------------------------------------------------------------------ producer (the query tile is on its way)
     // One thread does all of this next to the softmax warps, so every instruction counts: the page size is a
     // power of two (shifts and masks, no division), and the keys go out before anything else is looked at.
     const int box = page_size < ATC_KEYS ? page_size : ATC_KEYS;  // rows one copy brings
@@ -595,7 +602,7 @@ attention_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, cons
                             const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
                             const int* __restrict__ positions, const int* __restrict__ slot_of_token,
                             const int* __restrict__ block_table, int max_pages, int num_pages, int hq, int hkv,
-                            int page_size, int window, float scale_log2, int num_runs, int alone, float* __restrict__ scratch,
+                            int page_size, int window, float scale_log2, int num_runs, int run_tiles, int alone, float* __restrict__ scratch,
                             int* __restrict__ counters) {
   constexpr int PANELS = HD / 64;          // 64-column panels of Q, K and V
   constexpr int PANEL_BYTES = 128 * 128;   // 128 rows of 128 bytes
@@ -625,8 +632,10 @@ attention_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const int first_key = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
   const int item_lo = first_key / ATC_KEYS, tile_hi = pos_last / ATC_KEYS;
   const int item_tiles = (slot >= 0 && nrows > 0) ? tile_hi - item_lo + 1 : 0;
-  // the item's key tiles in `num_runs` runs of equal length; blocks past the last run have nothing to do
-  const int chunk = (item_tiles + nruns - 1) / nruns;
+  // the item's key tiles in runs of equal length for different blocks: `num_runs` of them, or (run_tiles > 0) as many as
+  // keep a run at `run_tiles` tiles at most, so that only long items are cut; blocks past the last run have nothing to do
+  const int want = run_tiles > 0 ? min(nruns, max(1, (item_tiles + run_tiles - 1) / run_tiles)) : nruns;
+  const int chunk = (item_tiles + want - 1) / want;
   const int nsplit = chunk > 0 ? (item_tiles + chunk - 1) / chunk : 1;
   const int split = blockIdx.y % nruns;
   const bool active = split < nsplit;
@@ -634,7 +643,12 @@ attention_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const int ntiles = (active && chunk > 0) ? min(chunk, item_tiles - split * chunk) : 0;
   const int* table = block_table + (size_t)(slot >= 0 ? slot : 0) * max_pages;
 
-  if (tid == 0) {
+  // the copying thread sets the barriers up and sends for the query tiles at once (nothing else lies there), while the
+  // others clear the stages and tensor memory is taken
+  if (warp == 8 && lane == 0) {
+    asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_q) : "memory");
+    asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_k) : "memory");
+    asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_v) : "memory");
     atc_mbar_init(atc_smem(&sh->q_full), 1);
     for (int s = 0; s < 2; ++s) {
       atc_mbar_init(atc_smem(&sh->k_full[s]), 1);
@@ -648,6 +662,12 @@ attention_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, cons
     sh->abort_flag = 0;
     sh->group_bad[0] = sh->group_bad[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    if (ntiles > 0) {
+      atc_mbar_expect_tx(atc_smem(&sh->q_full), (has_b ? 2 : 1) * KV_BYTES);
+      for (int x = 0; x < (has_b ? 2 : 1); ++x)
+        for (int p = 0; p < PANELS; ++p)
+          atc_tma_2d(atc_smem(q_s + x * KV_BYTES + p * PANEL_BYTES), &map_q, (head_a + x) * HD + p * 64, row0, atc_smem(&sh->q_full));
+    }
   }
   // the key and value stages start as zeros: rows that no page holds are never copied, and what multiplies a
   // probability of zero must be finite
@@ -664,13 +684,7 @@ attention_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const unsigned tmem = sh->tmem_base;
 
   if (warp == 8 && lane == 0) {
-    // ------------------------------------------------------------------ producer
-    if (ntiles > 0) {
-      atc_mbar_expect_tx(atc_smem(&sh->q_full), (has_b ? 2 : 1) * KV_BYTES);
-      for (int x = 0; x < (has_b ? 2 : 1); ++x)
-        for (int p = 0; p < PANELS; ++p)
-          atc_tma_2d(atc_smem(q_s + x * KV_BYTES + p * PANEL_BYTES), &map_q, (head_a + x) * HD + p * 64, row0, atc_smem(&sh->q_full));
-    }
+    // ------------------------------------------------------------------ producer (the query tiles are on their way)
     // One thread does all of this next to the softmax warps, so every instruction counts: the page size is a
     // power of two (shifts and masks, no division), and the keys go out before anything else is looked at.
     const int box = page_size < ATC_KEYS ? page_size : ATC_KEYS;  // rows one copy brings
@@ -900,7 +914,7 @@ static int atc_make_map(CUtensorMap* map, const void* base, long long rows, int 
 static int atc_launch_single(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, const int* tile_row0,
                              const int* tile_rows, int num_tiles, const int* positions, const int* slot_of_token,
                              const int* block_table, int max_pages, int num_pages, int hq, int hkv, int page_size, int window,
-                             float scale, int splits, float* scratch, int* counters, cudaStream_t stream) {
+                             float scale, int splits, int run_tiles, float* scratch, int* counters, cudaStream_t stream) {
   const size_t smem = 1024 + 1024 + (size_t)16384 * 4;
   auto kern = attention_prefill_tc_single_kernel<64>;
   static bool configured = false;
@@ -913,7 +927,7 @@ static int atc_launch_single(const CUtensorMap& mq, const CUtensorMap& mk, const
   dim3 grid(hq, num_tiles * splits);
   kern<<<grid, ATC_THREADS, smem, stream>>>(mq, mk, mv, (__nv_bfloat16*)out, tile_row0, tile_rows, positions, slot_of_token,
                                             block_table, max_pages, num_pages, hq, hkv, page_size, window, scale * ATC_LOG2E,
-                                            splits, scratch, counters);
+                                            splits, run_tiles, scratch, counters);
   MS_LAUNCH_CHECK("attention_prefill_tc");
   return 0;
 }
@@ -922,7 +936,7 @@ template <int HD>
 static int atc_launch_pair(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, const int* tile_row0,
                            const int* tile_rows, int num_tiles, const int* positions, const int* slot_of_token,
                            const int* block_table, int max_pages, int num_pages, int hq, int hkv, int page_size, int window,
-                           float scale, int splits, int alone, float* scratch, int* counters, cudaStream_t stream) {
+                           float scale, int splits, int run_tiles, int alone, float* scratch, int* counters, cudaStream_t stream) {
   // two heads' Q, two stages of K and of V (194 KB at head size 128); never less than half an SM's shared memory, so
   // that a block has the SM and all of its tensor memory to itself
   size_t smem = 1024 + 1024 + (size_t)(HD / 64) * 16384 * 6;
@@ -940,7 +954,7 @@ static int atc_launch_pair(const CUtensorMap& mq, const CUtensorMap& mk, const C
   dim3 grid(hkv * (alone ? groups : (groups + 1) / 2), num_tiles * splits);
   kern<<<grid, ATC_PAIR_THREADS, smem, stream>>>(mq, mk, mv, (__nv_bfloat16*)out, tile_row0, tile_rows, positions, slot_of_token,
                                                  block_table, max_pages, num_pages, hq, hkv, page_size, window, scale * ATC_LOG2E,
-                                                 splits, alone, scratch, counters);
+                                                 splits, run_tiles, alone, scratch, counters);
   MS_LAUNCH_CHECK("attention_prefill_tc");
   return 0;
 }
@@ -991,7 +1005,8 @@ MS_API long long ms_attention_prefill_tc_scratch_words(int num_tiles, int hq, in
 // How a launch is laid out so that it fills the GPU: few tiles of rows (a short prompt, a portion of a long one) would
 // leave most SMs idle behind the blocks with the longest rows of key tiles.  plan[0]: the number of runs the key tiles
 // of every item are cut into for different blocks (1 to 4).  plan[1]: 1 if, at head size 128, every block should take
-// one head instead of two of a group.  `max_keys`: the most keys any row of the launch sees; `total_key_tiles`: the
+// one head instead of two of a group.  plan[2]: if not 0, the most key tiles of a run (only longer items are cut).
+// `max_keys`: the most keys any row of the launch sees; `total_key_tiles`: the
 // tiles of 128 keys that the launch's tiles of rows see, in all (0: every tile sees max_keys).
 //
 // Head size 64 (two blocks per SM): as many runs as fill the places, at least four key tiles a run.
@@ -1007,6 +1022,7 @@ MS_API void ms_attention_prefill_tc_plan(int num_tiles, int hq, int hkv, int hd,
   if (num_tiles <= 0 || hq <= 0 || hkv <= 0 || sm_count <= 0) return;
   const int groups = hq / hkv;
   const int key_tiles = (max_keys + ATC_KEYS - 1) / ATC_KEYS;
+  plan[2] = 0;
   if (hd == 64) {
     const long long blocks = (long long)num_tiles * hq;
     int splits = (int)(2LL * sm_count / blocks);
@@ -1033,6 +1049,8 @@ MS_API void ms_attention_prefill_tc_plan(int num_tiles, int hq, int hkv, int hd,
         best = t;
         plan[0] = s;
         plan[1] = alone;
+        // blocks of very different lengths (a prompt taken whole): only items longer than a run are cut
+        plan[2] = (s > 1 && !alike) ? (key_tiles + s - 1) / s : 0;
       }
     }
   }
@@ -1041,18 +1059,19 @@ MS_API void ms_attention_prefill_tc_plan(int num_tiles, int hq, int hkv, int hd,
 // As ms_attention_prefill, with tiles of up to 128 rows.  q, out: bfloat16 [total_rows, hq*hd].  `splits` (1 to 4): the
 // key tiles of every item go to that many blocks, which meet in `scratch` (ms_attention_prefill_tc_scratch_words) and
 // count themselves in `counters` (num_tiles * hq of them, all zero).  `alone` (head size 128): a block takes one head, not two.
+// `run_tiles` > 0: an item is cut only into as many runs as keep a run at that many key tiles at most (0: always `splits`).
 MS_API int ms_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, void* out, int total_rows,
                                    const int* tile_row0, const int* tile_rows, int num_tiles, const int* positions,
                                    const int* slot_of_token, const int* block_table, int max_pages, int num_pages, int hq,
                                    int hkv, int hd, int page_size, int window, float scale, int splits, int alone,
-                                   float* scratch, long long scratch_words, int* counters, long long num_counters,
-                                   cudaStream_t stream) {
+                                   int run_tiles, float* scratch, long long scratch_words, int* counters,
+                                   long long num_counters, cudaStream_t stream) {
   if (num_tiles == 0) return 0;
   MS_REQUIRE(num_tiles > 0 && total_rows > 0 && hq > 0 && hkv > 0 && hq % hkv == 0, "attention_prefill_tc: bad sizes");
   MS_REQUIRE(ms_attention_prefill_tc_supports(hd, page_size),
              "attention_prefill_tc: head_dim %d (64 or 128) or page size %d (a power of two from 8) is not covered", hd, page_size);
   MS_REQUIRE(((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)out) % 16 == 0, "attention_prefill_tc: operands must be 16-byte aligned");
-  MS_REQUIRE(splits >= 1 && splits <= ATC_MAX_SPLITS, "attention_prefill_tc: %d splits (1 to %d)", splits, ATC_MAX_SPLITS);
+  MS_REQUIRE(splits >= 1 && splits <= ATC_MAX_SPLITS && run_tiles >= 0, "attention_prefill_tc: %d splits (1 to %d)", splits, ATC_MAX_SPLITS);
   const long long need = ms_attention_prefill_tc_scratch_words(num_tiles, hq, hd, splits);
   MS_REQUIRE(need == 0 || (scratch != nullptr && scratch_words >= need),
              "attention_prefill_tc: %d splits need %lld words of scratch memory, %lld were given", splits, need, scratch_words);
@@ -1066,7 +1085,7 @@ MS_API int ms_attention_prefill_tc(const void* q, const void* k_pages, const voi
   if (int rc = atc_make_map(&mv, v_pages, cache_rows, hd, hd, box)) return rc;
   if (hd == 64)
     return atc_launch_single(mq, mk, mv, out, tile_row0, tile_rows, num_tiles, positions, slot_of_token, block_table, max_pages,
-                             num_pages, hq, hkv, page_size, window, scale, splits, scratch, counters, stream);
+                             num_pages, hq, hkv, page_size, window, scale, splits, run_tiles, scratch, counters, stream);
   return atc_launch_pair<128>(mq, mk, mv, out, tile_row0, tile_rows, num_tiles, positions, slot_of_token, block_table, max_pages,
-                              num_pages, hq, hkv, page_size, window, scale, splits, alone ? 1 : 0, scratch, counters, stream);
+                              num_pages, hq, hkv, page_size, window, scale, splits, run_tiles, alone ? 1 : 0, scratch, counters, stream);
 }

@@ -75,7 +75,7 @@ class _Signatures:
     ms_attention_decode = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P]
     ms_attention_decode_cluster = [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, I, I, P]
     ms_attention_decode_cluster_rope = [P, I, P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, I, I, P]
-    ms_attention_prefill_tc = [P, P, P, P, I, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, LL, P, LL, P]
+    ms_attention_prefill_tc = [P, P, P, P, I, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, LL, P, LL, P]
     ms_attention_prefill_tc_plan = [I, I, I, I, I, I, I, P]
     ms_attention_prefill = [P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P]
     ms_gemm_small_m = [P, I, P, P, I, I, I, I, I, I, P]
@@ -746,13 +746,14 @@ def attention_prefill_tc_supports(head_dim: int, page_size: int) -> bool:
 
 def attention_prefill_tc_plan(num_tiles: int, num_heads: int, num_kv_heads: int, head_dim: int, max_keys: int,
                               key_tiles: int = 0):
-    """(splits, alone): into how many runs the kernel should cut every item's key tiles so that the launch fills the
-    GPU (1 to 4), and whether, at head size 128, every block should take one head instead of two of a group.
+    """(splits, alone, run_tiles): into how many runs the kernel should cut an item's key tiles so that the launch fills
+    the GPU (1 to 4), whether, at head size 128, every block should take one head instead of two of a group, and (if
+    not 0) the most key tiles of a run, so that only longer items are cut.
     `key_tiles`: the tiles of 128 keys that the launch's tiles of rows see, in all (0: every tile sees `max_keys`)."""
-    plan = (ctypes.c_int * 2)()
+    plan = (ctypes.c_int * 3)()
     lib().ms_attention_prefill_tc_plan(int(num_tiles), int(num_heads), int(num_kv_heads), int(head_dim), int(max_keys),
                                        int(key_tiles), sm_count(), plan)
-    return int(plan[0]), bool(plan[1])
+    return int(plan[0]), bool(plan[1]), int(plan[2])
 
 
 def attention_prefill_tc_scratch_words(num_tiles: int, num_heads: int, head_dim: int, splits: int) -> int:
@@ -764,13 +765,15 @@ def attention_prefill_tc_scratch_words(num_tiles: int, num_heads: int, head_dim:
 
 
 def attention_prefill_tc(q, k_pages, v_pages, out, tile_row0, tile_rows, num_tiles, positions, slot_of_token, block_table,
-                         num_heads, num_kv_heads, head_dim, window, scale, splits=1, scratch=None, counters=None, alone=False):
+                         num_heads, num_kv_heads, head_dim, window, scale, splits=1, scratch=None, counters=None, alone=False,
+                         run_tiles=0):
     """Paged causal attention for tiles of up to 128 consecutive rows of one sequence on tcgen05 tensor cores
     (TMA-fed, scores in tensor memory and taken into registers a row per thread, probabilities back into tensor
     memory, outputs accumulated there over all key tiles).  Head sizes 64 (one head per block) and 128 (two heads of a
     group per block, which share the keys and values), page sizes 8, 16, 32, ...  With `splits` > 1 the key tiles of
     every (tile, head) go to that many blocks, which meet in `scratch` (float32) and count themselves in `counters`
-    (int32, num_tiles * num_heads of them, all zero before and after).  `alone` (head size 128): one head per block."""
+    (int32, num_tiles * num_heads of them, all zero before and after).  `alone` (head size 128): one head per block.
+    `run_tiles` > 0: only items with more key tiles are cut, into runs of at most that many."""
     _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16,
           "attention_prefill_tc: bfloat16 only")
     _need(q.is_contiguous() and out.is_contiguous() and k_pages.is_contiguous() and v_pages.is_contiguous(),
@@ -785,7 +788,7 @@ def attention_prefill_tc(q, k_pages, v_pages, out, tile_row0, tile_rows, num_til
         lib().ms_attention_prefill_tc(
             _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), q.shape[0], _ptr(tile_row0), _ptr(tile_rows), int(num_tiles),
             _ptr(positions), _ptr(slot_of_token), _ptr(block_table), block_table.shape[1], k_pages.shape[0], num_heads,
-            num_kv_heads, head_dim, k_pages.shape[2], int(window or 0), float(scale), int(splits), 1 if alone else 0, _ptr(scratch),
+            num_kv_heads, head_dim, k_pages.shape[2], int(window or 0), float(scale), int(splits), 1 if alone else 0, int(run_tiles), _ptr(scratch),
             scratch.numel() if scratch is not None else 0, _ptr(counters), counters.numel() if counters is not None else 0,
             _stream(),
         ),

@@ -295,7 +295,7 @@ class Attention(Mixer):
             max_keys = work.shape[1] * self.CONTEXT_BUCKET
             if self.window:
                 max_keys = min(max_keys, self.window + self.BIG_TILE)
-            splits, alone = ops.attention_prefill_tc_plan(n_tiles, self.hq, self.hkv, self.hd, max_keys, work.shape[2] * n_tiles)
+            splits, alone, run_tiles = ops.attention_prefill_tc_plan(n_tiles, self.hq, self.hkv, self.hd, max_keys, work.shape[2] * n_tiles)
             scratch = counters = None
             if splits > 1:
                 words = ops.attention_prefill_tc_scratch_words(n_tiles, self.hq, self.hd, splits)
@@ -305,7 +305,7 @@ class Attention(Mixer):
             ops.attention_prefill_tc(
                 q, cache.k_pages, cache.v_pages, out, lists["big_tile_row0"], lists["big_tile_rows"], n_tiles,
                 ctx.positions, ctx.slot_of_token, table, self.hq, self.hkv, self.hd, self.window, self.scale, splits, scratch, counters,
-                alone=alone,
+                alone=alone, run_tiles=run_tiles,
             )
         elif sizes["tile_row0"]:
             ops.attention_prefill(

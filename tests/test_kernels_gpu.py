@@ -437,12 +437,14 @@ TC_ATT_CASES = [
 ]
 
 
-@pytest.mark.parametrize("splits,alone", [(1, False), (2, False), (3, False), (4, False), (1, True), (3, True)])
+@pytest.mark.parametrize("splits,alone,run_tiles", [(1, False, 0), (2, False, 0), (3, False, 0), (4, False, 0), (1, True, 0), (3, True, 0),
+                                                    (2, False, 2), (4, False, 1), (3, True, 2)])
 @pytest.mark.parametrize("lens,hq,hkv,hd,page,window", TC_ATT_CASES)
-def test_attention_prefill_tc(lens, hq, hkv, hd, page, window, splits, alone):
+def test_attention_prefill_tc(lens, hq, hkv, hd, page, window, splits, alone, run_tiles):
     """The tcgen05 kernel for portions of prompts: tiles of up to 128 rows, pages of several sizes, windows; the key
     tiles of every (tile, head) in one run or split over two to four blocks that merge through scratch memory; at
-    head size 128 two heads of a group per block, or one (`alone`).  Run twice on the same scratch memory: a launch
+    head size 128 two heads of a group per block, or one (`alone`); every item cut, or only those with more than
+    `run_tiles` key tiles.  Run twice on the same scratch memory: a launch
     leaves its counters as it found them."""
     import torch
     from machserve_b200 import ops
@@ -470,7 +472,7 @@ def test_attention_prefill_tc(lens, hq, hkv, hd, page, window, splits, alone):
         out = torch.full((len(rows), hq * hd), 7.0, dtype=torch.bfloat16, device=dev())
         ops.attention_prefill_tc(T(q, torch.bfloat16), case.k_pages, case.v_pages, out, T(np.array(tile0, dtype=np.int32)),
                                  T(np.array(tilen, dtype=np.int32)), len(tile0), pos, slot, case.table, hq, hkv, hd, window,
-                                 hd ** -0.5, splits, scratch, counters, alone=alone)
+                                 hd ** -0.5, splits, scratch, counters, alone=alone, run_tiles=run_tiles)
         assert ops.gemm_tc_status() == 0
         err = np.abs(N(out) - want).max(axis=1)
         assert err.max() <= 2.0 ** -7 * max(1.0, np.abs(want).max()), f"worst row {int(err.argmax())} of {len(rows)}: {rows[int(err.argmax())]}"
@@ -489,17 +491,17 @@ def test_attention_prefill_tc(lens, hq, hkv, hd, page, window, splits, alone):
 def test_attention_prefill_tc_split_policy():
     """Few tiles of rows against many keys are split; a launch that fills the GPU by itself is not."""
     from machserve_b200 import ops
-    assert ops.attention_prefill_tc_plan(64, 14, 2, 64, 8192) == (1, False)
-    assert ops.attention_prefill_tc_plan(4, 14, 2, 64, 2048) == (4, False)
-    assert ops.attention_prefill_tc_plan(16, 14, 2, 64, 2048) == (1, False)  # 224 blocks for 296 places
+    assert ops.attention_prefill_tc_plan(64, 14, 2, 64, 8192)[:2] == (1, False)
+    assert ops.attention_prefill_tc_plan(4, 14, 2, 64, 2048)[:2] == (4, False)
+    assert ops.attention_prefill_tc_plan(16, 14, 2, 64, 2048, 136) == (1, False, 0)  # 224 blocks for 296 places
     # head size 128, by the model of the launch's time
-    assert ops.attention_prefill_tc_plan(64, 12, 2, 128, 8192, 2080) == (1, False)  # a long prompt whole: two heads a block
-    assert ops.attention_prefill_tc_plan(16, 12, 2, 128, 2048, 136) == (2, False)   # 96 blocks, the longest of 16 key tiles
-    assert ops.attention_prefill_tc_plan(32, 28, 4, 128, 4096) == (1, False)        # 512 blocks: nothing to gain
-    assert ops.attention_prefill_tc_plan(4, 28, 4, 128, 4096, 122) == (2, False)    # 64 blocks of equal length: 128, not 192
-    assert ops.attention_prefill_tc_plan(4, 12, 2, 128, 2048, 58) == (3, True)      # 24 blocks: 48 of one head, in 3 runs
-    assert ops.attention_prefill_tc_plan(4, 12, 2, 128, 512, 10) == (1, True)       # too few keys to split
-    assert ops.attention_prefill_tc_plan(1, 2, 1, 64, 1024) == (2, False)
+    assert ops.attention_prefill_tc_plan(64, 12, 2, 128, 8192, 2080)[:2] == (1, False)  # a long prompt whole: two heads a block
+    assert ops.attention_prefill_tc_plan(16, 12, 2, 128, 2048, 136) == (2, False, 8)    # 96 blocks, the longest of 16 key tiles: those of more than 8 in two runs
+    assert ops.attention_prefill_tc_plan(32, 28, 4, 128, 4096)[:2] == (1, False)        # 512 blocks: nothing to gain
+    assert ops.attention_prefill_tc_plan(4, 28, 4, 128, 4096, 122)[:2] == (2, False)    # 64 blocks of equal length: 128, not 192
+    assert ops.attention_prefill_tc_plan(4, 12, 2, 128, 2048, 58)[:2] == (3, True)      # 24 blocks: 48 of one head, in 3 runs
+    assert ops.attention_prefill_tc_plan(4, 12, 2, 128, 512, 10)[:2] == (1, True)       # too few keys to split
+    assert ops.attention_prefill_tc_plan(1, 2, 1, 64, 1024)[:2] == (2, False)
 
 
 @pytest.mark.parametrize("k_gain", [None, 48.0])
