@@ -2,10 +2,11 @@
 // float32 path and is the fallback of the bfloat16 path for sizes the fast
 // kernels refuse.
 //
-// One block of four warps per (token, query head).  The keys a token sees,
+// One block of W warps per (token, query head): eight for head sizes up to 64, four above (a constant of the model, so
+// that every step shape computes a token the same way).  The keys a token sees,
 // [max(0, pos - window + 1), pos], are cut into tiles of 32 keys that start at
-// absolute multiples of 32; warp w takes tiles w, w+4, ... in ascending order with
-// an online softmax, and the four partial results are merged in warp order.  So the
+// absolute multiples of 32; warp w takes tiles w, w+W, ... in ascending order with
+// an online softmax, and the W partial results are merged in warp order.  So the
 // arithmetic for a token depends on its position alone: not on how the sequence was
 // cut into steps, not on what else is in the batch, not on which pages hold the keys.
 // A warp brings its tile of keys into shared memory row by row (every load a whole row,
@@ -19,10 +20,10 @@
 // read.  Cache layout: pages[page][kv_head][slot in page][head_dim].
 #include "common.cuh"
 
-#define ATT_WARPS 4
+#define ATT_MAX_WARPS 8
 #define ATT_MAX_HD 256
 
-template <typename TA, typename TC>
+template <typename TA, typename TC, int ATT_WARPS>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 attention_generic_kernel(const TA* __restrict__ q, const TC* __restrict__ k_pages, const TC* __restrict__ v_pages,
                          TA* __restrict__ out, const int* __restrict__ positions,
@@ -155,19 +156,25 @@ MS_API int ms_attention_generic(const void* q, const void* k_pages, const void* 
   MS_REQUIRE(hd > 0 && hd <= ATT_MAX_HD, "attention: head_dim %d is outside (0, %d]", hd, ATT_MAX_HD);
   MS_REQUIRE(page_size > 0 && max_pages > 0 && num_pages > 0, "attention: bad cache sizes");
   const unsigned blocks = (unsigned)tokens * (unsigned)hq;
-  const size_t smem = (size_t)ATT_WARPS * 32 * (hd + 1) * sizeof(float);
-#define MS_ATT_CASE(TA, TC)                                                                                     \
+#define MS_ATT_LAUNCH(TA, TC, W)                                                                                \
   do {                                                                                                          \
-    static bool configured = false;                                                                             \
-    if (!configured) {                                                                                          \
-      cudaError_t e = cudaFuncSetAttribute(attention_generic_kernel<TA, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                           (int)((size_t)ATT_WARPS * 32 * (ATT_MAX_HD + 1) * sizeof(float)));   \
+    const size_t smem = (size_t)(W) * 32 * (hd + 1) * sizeof(float);                                           \
+    static size_t configured = 0;                                                                               \
+    if (smem > configured) {                                                                                    \
+      cudaError_t e = cudaFuncSetAttribute(attention_generic_kernel<TA, TC, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
       MS_REQUIRE(e == cudaSuccess, "attention: cannot get shared memory for the key tiles: %s", cudaGetErrorString(e)); \
-      configured = true;                                                                                        \
+      configured = smem;                                                                                        \
     }                                                                                                           \
-    attention_generic_kernel<TA, TC><<<blocks, ATT_WARPS * 32, smem, stream>>>(                                \
+    attention_generic_kernel<TA, TC, W><<<blocks, (W) * 32, smem, stream>>>(                                   \
         (const TA*)q, (const TC*)k_pages, (const TC*)v_pages, (TA*)out, positions, seq_of_token, block_table,  \
         max_pages, num_pages, hq, hkv, hd, page_size, window, scale);                                          \
+  } while (0)
+#define MS_ATT_CASE(TA, TC)                \
+  do {                                     \
+    if (hd <= 64)                          \
+      MS_ATT_LAUNCH(TA, TC, ATT_MAX_WARPS); \
+    else                                   \
+      MS_ATT_LAUNCH(TA, TC, 4);            \
   } while (0)
   if (act_dtype == MS_F32 && cache_dtype == MS_F32)
     MS_ATT_CASE(float, float);
@@ -178,6 +185,7 @@ MS_API int ms_attention_generic(const void* q, const void* k_pages, const void* 
   else
     MS_REQUIRE(false, "attention: unsupported dtypes act=%d cache=%d", act_dtype, cache_dtype);
 #undef MS_ATT_CASE
+#undef MS_ATT_LAUNCH
   MS_LAUNCH_CHECK("attention_generic");
   return 0;
 }

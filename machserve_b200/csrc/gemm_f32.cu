@@ -71,38 +71,56 @@ gemm_f32_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ 
 #define G32S_COLS 8
 #define G32S_KT 128
 
+// Four bytes from global to shared memory without passing through registers; `valid` false: a zero instead.
+__device__ __forceinline__ void g32_cp_async4(float* smem, const float* gmem, bool valid) {
+  const int n = valid ? 4 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem), "r"(n));
+}
+
 __global__ void __launch_bounds__(G32S_ROWS * G32S_COLS)
 gemm_f32_small_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ w, const float* __restrict__ bias,
                       float* __restrict__ out, int ldo, int M, int N, int K) {
-  __shared__ __align__(16) float ws[G32S_COLS][G32S_KT + 4];
-  __shared__ __align__(16) float xs[G32S_ROWS][G32S_KT + 4];
+  // two stages: the copies of the next 128 k are on their way while this thread adds up the present ones
+  __shared__ __align__(16) float ws[2][G32S_COLS][G32S_KT + 4];
+  __shared__ __align__(16) float xs[2][G32S_ROWS][G32S_KT + 4];
   const int tid = threadIdx.x, nl = tid >> 4, m = tid & 15;
   const int n0 = blockIdx.x * G32S_COLS;
-  float acc = 0.f;
-  for (int k0 = 0; k0 < K; k0 += G32S_KT) {
+  auto request = [&](int stage, int k0) {
+    const int gk = k0 + tid;
 #pragma unroll
     for (int i = 0; i < G32S_COLS; ++i) {  // 8 x 128 weights: a row of 128 consecutive k per 128 threads
-      const int gk = k0 + tid;
-      ws[i][tid] = (n0 + i < N && gk < K) ? w[(size_t)(n0 + i) * K + gk] : 0.f;
+      const bool ok = n0 + i < N && gk < K;
+      g32_cp_async4(&ws[stage][i][tid], ok ? w + (size_t)(n0 + i) * K + gk : w, ok);
     }
 #pragma unroll
     for (int i = 0; i < G32S_ROWS; ++i) {
-      const int gk = k0 + tid;
-      xs[i][tid] = (i < M && gk < K) ? x[(size_t)i * ldx + gk] : 0.f;
+      const bool ok = i < M && gk < K;
+      g32_cp_async4(&xs[stage][i][tid], ok ? x + (size_t)i * ldx + gk : x, ok);
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
+  };
+  float acc = 0.f;
+  request(0, 0);
+  for (int k0 = 0, stage = 0; k0 < K; k0 += G32S_KT, stage ^= 1) {
+    if (k0 + G32S_KT < K) {
+      request(stage ^ 1, k0 + G32S_KT);
+      asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     }
     __syncthreads();
     const int kn = K - k0 < G32S_KT ? K - k0 : G32S_KT;
     int c = 0;
     for (; c + 4 <= kn; c += 4) {
-      const float4 a = *reinterpret_cast<const float4*>(&xs[m][c]);
-      const float4 b = *reinterpret_cast<const float4*>(&ws[nl][c]);
+      const float4 a = *reinterpret_cast<const float4*>(&xs[stage][m][c]);
+      const float4 b = *reinterpret_cast<const float4*>(&ws[stage][nl][c]);
       acc = fmaf(a.x, b.x, acc);
       acc = fmaf(a.y, b.y, acc);
       acc = fmaf(a.z, b.z, acc);
       acc = fmaf(a.w, b.w, acc);
     }
-    for (; c < kn; ++c) acc = fmaf(xs[m][c], ws[nl][c], acc);
-    __syncthreads();
+    for (; c < kn; ++c) acc = fmaf(xs[stage][m][c], ws[stage][nl][c], acc);
+    __syncthreads();  // all are done with this stage before the copies after the next are requested into it
   }
   const int n = n0 + nl;
   if (m < M && n < N) out[(size_t)m * ldo + n] = acc + (bias ? bias[n] : 0.f);
