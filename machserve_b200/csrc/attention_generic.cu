@@ -146,35 +146,258 @@ attention_generic_kernel(const TA* __restrict__ q, const TC* __restrict__ k_page
   }
 }
 
-// q, out: [tokens, hq*hd].  window <= 0: every earlier key is visible.
+// The same arithmetic for R consecutive rows of a step per block (portions of prompts): rows of one sequence whose
+// ranges of keys begin in the same tile share every tile of keys and values that a warp stages, so the cache is read
+// once for R rows instead of once for each; row by row, each warp does exactly what it does in the kernel above (its
+// tiles, its order of sums, the merge in warp order), so a row's result is the same bit for bit whichever kernel
+// computed it and whatever rows stood beside it.  NACC: head_dim / 32 rounded up.
+#define ATT_ROWS 8
+
+template <typename TA, typename TC, int ATT_WARPS, int NACC>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+attention_generic_rows_kernel(const TA* __restrict__ q, const TC* __restrict__ k_pages, const TC* __restrict__ v_pages,
+                              TA* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                              const int* __restrict__ block_table, int max_pages, int num_pages, int tokens, int hq, int hkv, int hd,
+                              int page_size, int window, float scale) {
+  extern __shared__ float rows_smem[];
+  // [R][hd] queries; [warp][32][hd + 1] keys; [warp][32][hd] values; [warp][R][hd + 2] partial results for the merge
+  float* q_s = rows_smem;
+  float* k_all = q_s + ATT_ROWS * hd;
+  float* v_all = k_all + (size_t)ATT_WARPS * 32 * (hd + 1);
+  float* part = v_all + (size_t)ATT_WARPS * 32 * hd;
+  const int group = blockIdx.x / hq, h = blockIdx.x - group * hq;
+  const int t0 = group * ATT_ROWS;
+  const int kvh = h / (hq / hkv);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const size_t head_off = (size_t)kvh * page_size * hd;
+  const size_t page_elems = (size_t)hkv * page_size * hd;
+  float* my_k = k_all + (size_t)warp * 32 * (hd + 1);
+  float* my_v = v_all + (size_t)warp * 32 * hd;
+
+  int seq[ATT_ROWS], pos[ATT_ROWS], first[ATT_ROWS];
+#pragma unroll
+  for (int r = 0; r < ATT_ROWS; ++r) {
+    const int t = t0 + r;
+    seq[r] = t < tokens ? seq_of_token[t] : -1;
+    pos[r] = seq[r] >= 0 ? positions[t] : -1;
+    first[r] = (window > 0 && pos[r] - window + 1 > 0) ? pos[r] - window + 1 : 0;
+  }
+  for (int e = threadIdx.x; e < ATT_ROWS * hd; e += blockDim.x) {
+    const int r = e / hd, d = e - r * hd;
+    q_s[e] = t0 + r < tokens ? ms_to_float(q[((size_t)(t0 + r) * hq + h) * hd + d]) : 0.f;
+  }
+  __syncthreads();
+
+  float m[ATT_ROWS], l[ATT_ROWS], acc[ATT_ROWS][NACC];
+#pragma unroll
+  for (int r = 0; r < ATT_ROWS; ++r) {
+    m[r] = -INFINITY;
+    l[r] = 0.f;
+#pragma unroll
+    for (int i = 0; i < NACC; ++i) acc[r][i] = 0.f;
+  }
+
+  // runs of rows that share their tiles: the same sequence and the same first tile
+  unsigned done = 0;
+#pragma unroll 1
+  for (int lead = 0; lead < ATT_ROWS; ++lead) {
+    if ((done >> lead) & 1u) continue;
+    int lead_seq = -1, lead_tile = 0;
+#pragma unroll
+    for (int r = 0; r < ATT_ROWS; ++r)
+      if (r == lead) {
+        lead_seq = seq[r];
+        lead_tile = first[r] / 32;
+      }
+    unsigned run = 0;
+    int lo_key = 0x7fffffff, hi_pos = -1;
+#pragma unroll
+    for (int r = 0; r < ATT_ROWS; ++r)
+      if (r >= lead && seq[r] == lead_seq && first[r] / 32 == lead_tile && !((done >> r) & 1u)) {
+        run |= 1u << r;
+        lo_key = min(lo_key, first[r]);
+        hi_pos = max(hi_pos, pos[r]);
+      }
+    done |= run;
+    if (lead_seq < 0) continue;  // padding rows
+    const int* table = block_table + (size_t)lead_seq * max_pages;
+#pragma unroll 1
+    for (int tile = lead_tile + warp; tile * 32 <= hi_pos; tile += ATT_WARPS) {
+      const int key = tile * 32 + lane;
+      long long base = -1;  // element offset of this lane's key row inside the pages (for any row of the run)
+      if (key >= lo_key && key <= hi_pos) {
+        const int page = table[key / page_size];
+        if (page >= 0 && page < num_pages) base = (long long)((size_t)page * page_elems + head_off + (size_t)(key % page_size) * hd);
+      }
+      __syncwarp();  // the tile before has been read
+      for (int j0 = 0; j0 < 32; j0 += 8) {
+        long long b[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) b[u] = __shfl_sync(0xffffffffu, base, j0 + u);
+        for (int d = lane; d < hd; d += 32) {
+          float kv[8], vv[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            kv[u] = b[u] >= 0 ? ms_to_float(k_pages[b[u] + d]) : 0.f;
+            vv[u] = b[u] >= 0 ? ms_to_float(v_pages[b[u] + d]) : 0.f;
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            my_k[(j0 + u) * (hd + 1) + d] = kv[u];
+            my_v[(j0 + u) * hd + d] = vv[u];
+          }
+        }
+      }
+      __syncwarp();
+      const float* kr = my_k + lane * (hd + 1);
+      // the rows' dot products side by side (each row's own chain of sums in the order of the kernel above; eight
+      // chains keep the multiply-add units busy where one would wait for itself)
+      float dot[ATT_ROWS];
+#pragma unroll
+      for (int r = 0; r < ATT_ROWS; ++r) dot[r] = 0.f;
+      if ((hd & 3) == 0) {
+        for (int d = 0; d < hd; d += 4) {
+          const float k0 = kr[d], k1 = kr[d + 1], k2 = kr[d + 2], k3 = kr[d + 3];
+#pragma unroll
+          for (int r = 0; r < ATT_ROWS; ++r) {
+            const float4 qv = *reinterpret_cast<const float4*>(q_s + r * hd + d);
+            dot[r] = fmaf(qv.x, k0, dot[r]);
+            dot[r] = fmaf(qv.y, k1, dot[r]);
+            dot[r] = fmaf(qv.z, k2, dot[r]);
+            dot[r] = fmaf(qv.w, k3, dot[r]);
+          }
+        }
+      } else {
+        for (int d = 0; d < hd; ++d) {
+          const float kd = kr[d];
+#pragma unroll
+          for (int r = 0; r < ATT_ROWS; ++r) dot[r] = fmaf(q_s[r * hd + d], kd, dot[r]);
+        }
+      }
+      float pr[ATT_ROWS];
+      unsigned vmask[ATT_ROWS];
+#pragma unroll
+      for (int r = 0; r < ATT_ROWS; ++r) {
+        pr[r] = 0.f;
+        vmask[r] = 0u;
+        if (!((run >> r) & 1u) || tile * 32 > pos[r]) continue;  // (the same for the whole warp)
+        const bool valid = base >= 0 && key >= first[r] && key <= pos[r];
+        const float sc = valid ? dot[r] * scale : -INFINITY;
+        const float tile_max = ms_warp_max(sc);
+        const float m_new = fmaxf(m[r], tile_max);
+        pr[r] = (valid && m_new > -INFINITY) ? expf(sc - m_new) : 0.f;
+        const float corr = (m[r] == -INFINITY) ? 0.f : expf(m[r] - m_new);
+        l[r] = l[r] * corr + ms_warp_sum(pr[r]);
+#pragma unroll
+        for (int i = 0; i < NACC; ++i) acc[r][i] *= corr;
+        vmask[r] = __ballot_sync(0xffffffffu, valid);
+        m[r] = m_new;
+      }
+      // the values key by key in ascending order, as the kernel above adds them; a value serves all rows
+      for (int j = 0; j < 32; ++j) {
+        float vj[NACC];
+#pragma unroll
+        for (int i = 0; i < NACC; ++i) {
+          const int d = lane + 32 * i;
+          vj[i] = d < hd ? my_v[j * hd + d] : 0.f;
+        }
+#pragma unroll
+        for (int r = 0; r < ATT_ROWS; ++r) {
+          const float pj = __shfl_sync(0xffffffffu, pr[r], j);
+          if ((vmask[r] >> j) & 1u) {
+#pragma unroll
+            for (int i = 0; i < NACC; ++i) acc[r][i] = fmaf(pj, vj[i], acc[r][i]);
+          }
+        }
+      }
+    }
+  }
+
+  // every row's partial results of all warps, then warp r merges row r (and r + W, ...) in warp order
+  __syncthreads();
+  const int pw = hd + 2;
+#pragma unroll
+  for (int r = 0; r < ATT_ROWS; ++r) {
+    float* p = part + ((size_t)warp * ATT_ROWS + r) * pw;
+#pragma unroll
+    for (int i = 0; i < NACC; ++i) {
+      const int d = lane + 32 * i;
+      if (d < hd) p[d] = acc[r][i];
+    }
+    if (lane == 0) {
+      p[hd] = m[r];
+      p[hd + 1] = l[r];
+    }
+  }
+  __syncthreads();
+  for (int r = warp; r < ATT_ROWS; r += ATT_WARPS) {
+    const int t = t0 + r;
+    if (t >= tokens || seq_of_token[t] < 0) continue;
+    float mm = -INFINITY;
+    for (int w = 0; w < ATT_WARPS; ++w) mm = fmaxf(mm, part[((size_t)w * ATT_ROWS + r) * pw + hd]);
+    float f[ATT_WARPS], ll = 0.f;
+    for (int w = 0; w < ATT_WARPS; ++w) {
+      const float* p = part + ((size_t)w * ATT_ROWS + r) * pw;
+      f[w] = p[hd + 1] > 0.f ? expf(p[hd] - mm) : 0.f;
+      ll += p[hd + 1] * f[w];
+    }
+    const float inv = ll > 0.f ? 1.f / ll : 0.f;
+    for (int d = lane; d < hd; d += 32) {
+      float o = 0.f;
+      for (int w = 0; w < ATT_WARPS; ++w) o += part[((size_t)w * ATT_ROWS + r) * pw + d] * f[w];
+      out[((size_t)t * hq + h) * hd + d] = ms_from_float<TA>(o * inv);
+    }
+  }
+}
+
+// q, out: [tokens, hq*hd].  window <= 0: every earlier key is visible.  share_rows: the step has rows that follow one
+// another in a sequence (portions of prompts): eight rows a block share the tiles they read (head sizes up to 128);
+// the results are the same bits either way.
 MS_API int ms_attention_generic(const void* q, const void* k_pages, const void* v_pages, void* out, int act_dtype,
                                 int cache_dtype, const int* positions, const int* seq_of_token,
                                 const int* block_table, int max_pages, int num_pages, int tokens, int hq, int hkv,
-                                int hd, int page_size, int window, float scale, cudaStream_t stream) {
+                                int hd, int page_size, int window, float scale, int share_rows, cudaStream_t stream) {
   if (tokens == 0) return 0;
   MS_REQUIRE(tokens > 0 && hq > 0 && hkv > 0 && hq % hkv == 0, "attention: bad head counts hq=%d hkv=%d", hq, hkv);
   MS_REQUIRE(hd > 0 && hd <= ATT_MAX_HD, "attention: head_dim %d is outside (0, %d]", hd, ATT_MAX_HD);
   MS_REQUIRE(page_size > 0 && max_pages > 0 && num_pages > 0, "attention: bad cache sizes");
-  const unsigned blocks = (unsigned)tokens * (unsigned)hq;
+  const bool rows = share_rows && hd <= 128 && tokens > 1;
+  const unsigned blocks = rows ? (unsigned)((tokens + ATT_ROWS - 1) / ATT_ROWS) * (unsigned)hq : (unsigned)tokens * (unsigned)hq;
+#define MS_ATT_SET_SMEM(KERN, BYTES)                                                                            \
+  do {                                                                                                          \
+    static size_t configured = 0;                                                                               \
+    if ((BYTES) > configured) {                                                                                 \
+      cudaError_t e = cudaFuncSetAttribute(KERN, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(BYTES));    \
+      MS_REQUIRE(e == cudaSuccess, "attention: cannot get shared memory for the key tiles: %s", cudaGetErrorString(e)); \
+      configured = (BYTES);                                                                                     \
+    }                                                                                                           \
+  } while (0)
 #define MS_ATT_LAUNCH(TA, TC, W)                                                                                \
   do {                                                                                                          \
     const size_t smem = (size_t)(W) * 32 * (hd + 1) * sizeof(float);                                           \
-    static size_t configured = 0;                                                                               \
-    if (smem > configured) {                                                                                    \
-      cudaError_t e = cudaFuncSetAttribute(attention_generic_kernel<TA, TC, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-      MS_REQUIRE(e == cudaSuccess, "attention: cannot get shared memory for the key tiles: %s", cudaGetErrorString(e)); \
-      configured = smem;                                                                                        \
-    }                                                                                                           \
-    attention_generic_kernel<TA, TC, W><<<blocks, (W) * 32, smem, stream>>>(                                   \
-        (const TA*)q, (const TC*)k_pages, (const TC*)v_pages, (TA*)out, positions, seq_of_token, block_table,  \
-        max_pages, num_pages, hq, hkv, hd, page_size, window, scale);                                          \
+    auto kern = attention_generic_kernel<TA, TC, W>;                                                            \
+    MS_ATT_SET_SMEM(kern, smem);                                                                                \
+    kern<<<blocks, (W) * 32, smem, stream>>>((const TA*)q, (const TC*)k_pages, (const TC*)v_pages, (TA*)out, positions, \
+                                            seq_of_token, block_table, max_pages, num_pages, hq, hkv, hd, page_size, window, scale); \
   } while (0)
-#define MS_ATT_CASE(TA, TC)                \
-  do {                                     \
-    if (hd <= 64)                          \
-      MS_ATT_LAUNCH(TA, TC, ATT_MAX_WARPS); \
-    else                                   \
-      MS_ATT_LAUNCH(TA, TC, 4);            \
+#define MS_ATT_LAUNCH_ROWS(TA, TC, W, NACC)                                                                     \
+  do {                                                                                                          \
+    const size_t smem = ((size_t)ATT_ROWS * hd + (size_t)(W) * 32 * (2 * hd + 1) + (size_t)(W) * ATT_ROWS * (hd + 2)) * sizeof(float); \
+    auto kern = attention_generic_rows_kernel<TA, TC, W, NACC>;                                                 \
+    MS_ATT_SET_SMEM(kern, smem);                                                                                \
+    kern<<<blocks, (W) * 32, smem, stream>>>((const TA*)q, (const TC*)k_pages, (const TC*)v_pages, (TA*)out, positions, \
+                                            seq_of_token, block_table, max_pages, num_pages, tokens, hq, hkv, hd, page_size, window, scale); \
+  } while (0)
+#define MS_ATT_CASE(TA, TC)                           \
+  do {                                                \
+    if (rows && hd <= 64)                             \
+      MS_ATT_LAUNCH_ROWS(TA, TC, ATT_MAX_WARPS, 2);   \
+    else if (rows)                                    \
+      MS_ATT_LAUNCH_ROWS(TA, TC, 4, 4);               \
+    else if (hd <= 64)                                \
+      MS_ATT_LAUNCH(TA, TC, ATT_MAX_WARPS);           \
+    else                                              \
+      MS_ATT_LAUNCH(TA, TC, 4);                       \
   } while (0)
   if (act_dtype == MS_F32 && cache_dtype == MS_F32)
     MS_ATT_CASE(float, float);
@@ -186,6 +409,8 @@ MS_API int ms_attention_generic(const void* q, const void* k_pages, const void* 
     MS_REQUIRE(false, "attention: unsupported dtypes act=%d cache=%d", act_dtype, cache_dtype);
 #undef MS_ATT_CASE
 #undef MS_ATT_LAUNCH
+#undef MS_ATT_LAUNCH_ROWS
+#undef MS_ATT_SET_SMEM
   MS_LAUNCH_CHECK("attention_generic");
   return 0;
 }

@@ -8,56 +8,103 @@
 // (crates/mach-model/src/kernels.rs:5772-5798 of gqf2008/machserve).
 #include "common.cuh"
 
-#define G32_BM 64
-#define G32_BN 64
+#define G32_BM 128
+#define G32_BN 128
 #define G32_BK 16
 
+// Four bytes from global to shared memory without passing through registers; `valid` false: a zero instead.
+__device__ __forceinline__ void g32_cp_async4(float* smem, const float* gmem, bool valid) {
+  const int n = valid ? 4 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem), "r"(n));
+}
+
+// Sixteen bytes from global to shared memory without passing through registers; `valid` false: zeros instead.
+__device__ __forceinline__ void g32_cp_async16(float* smem, const float* gmem, bool valid) {
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem), "r"(n));
+}
+
+// A tile of 128 x 128 outputs per block of 256 threads, 8 x 8 per thread (rows tm, tm + 16, ..., columns tn, tn + 16, ...:
+// a quarter warp's 16-byte reads of rows 80 bytes apart fall into different banks), K in steps of 16 through two stages: the copies of the next
+// step are on their way while this one is multiplied.  The operands lie in shared memory as they lie in global memory
+// ([row][k], rows padded to 20 floats); every thread adds its products for k = 0..K-1 in ascending order.
+// VEC: K and the row strides are multiples of 4 and the bases 16-byte aligned (16-byte copies); else element by element.
+template <bool VEC>
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ w, const float* __restrict__ bias,
                 float* __restrict__ out, int ldo, int M, int N, int K) {
-  __shared__ float xs[G32_BK][G32_BM + 4];
-  __shared__ float ws[G32_BK][G32_BN + 4];
+  constexpr int LD = G32_BK + 4;
+  __shared__ __align__(16) float xs[2][G32_BM][LD];
+  __shared__ __align__(16) float ws[2][G32_BN][LD];
   const int m0 = blockIdx.y * G32_BM, n0 = blockIdx.x * G32_BN;
   const int tid = threadIdx.x;
-  const int tm = (tid / 16) * 4, tn = (tid % 16) * 4;  // this thread's 4x4 corner in the tile
-  float acc[4][4];
+  const int tm = tid / 16, tn = tid % 16;  // this thread's rows tm, tm + 16, ..., tm + 112; its columns tn, tn + 16, ...
+  float acc[8][8];
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
+  for (int i = 0; i < 8; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
 
-  for (int k0 = 0; k0 < K; k0 += G32_BK) {
-    // 64 rows x 16 k of each operand; four elements per thread
+  auto request = [&](int stage, int k0) {
+    if (VEC) {
+      // 128 rows x 16 k of each operand = 512 pieces of 16 bytes: two per thread
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int e = tid + i * 256;
-      const int r = e / G32_BK, kk = e % G32_BK;
-      const int gk = k0 + kk;
-      xs[kk][r] = (m0 + r < M && gk < K) ? x[(size_t)(m0 + r) * ldx + gk] : 0.f;
-      ws[kk][r] = (n0 + r < N && gk < K) ? w[(size_t)(n0 + r) * K + gk] : 0.f;
+      for (int i = 0; i < 2; ++i) {
+        const int e = tid + i * 256, r = e >> 2, kq = (e & 3) * 4;
+        const int gk = k0 + kq;
+        const bool xo = m0 + r < M && gk < K, wo = n0 + r < N && gk < K;
+        g32_cp_async16(&xs[stage][r][kq], xo ? x + (size_t)(m0 + r) * ldx + gk : x, xo);
+        g32_cp_async16(&ws[stage][r][kq], wo ? w + (size_t)(n0 + r) * K + gk : w, wo);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int e = tid + i * 256, r = e >> 4, kk = e & 15;
+        const int gk = k0 + kk;
+        const bool xo = m0 + r < M && gk < K, wo = n0 + r < N && gk < K;
+        g32_cp_async4(&xs[stage][r][kk], xo ? x + (size_t)(m0 + r) * ldx + gk : x, xo);
+        g32_cp_async4(&ws[stage][r][kk], wo ? w + (size_t)(n0 + r) * K + gk : w, wo);
+      }
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
+  };
+
+  request(0, 0);
+  for (int k0 = 0, stage = 0; k0 < K; k0 += G32_BK, stage ^= 1) {
+    if (k0 + G32_BK < K) {
+      request(stage ^ 1, k0 + G32_BK);
+      asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     }
     __syncthreads();
 #pragma unroll
-    for (int kk = 0; kk < G32_BK; ++kk) {
-      float a[4], b[4];
+    for (int kq = 0; kq < G32_BK; kq += 4) {
+      float4 a[8], b[8];  // four k of each of the thread's eight rows and eight columns
 #pragma unroll
-      for (int i = 0; i < 4; ++i) a[i] = xs[kk][tm + i];
+      for (int i = 0; i < 8; ++i) {
+        a[i] = *reinterpret_cast<const float4*>(&xs[stage][tm + 16 * i][kq]);
+        b[i] = *reinterpret_cast<const float4*>(&ws[stage][tn + 16 * i][kq]);
+      }
 #pragma unroll
-      for (int j = 0; j < 4; ++j) b[j] = ws[kk][tn + j];
+      for (int i = 0; i < 8; ++i)
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        for (int j = 0; j < 8; ++j) {
+          acc[i][j] = fmaf(a[i].x, b[j].x, acc[i][j]);
+          acc[i][j] = fmaf(a[i].y, b[j].y, acc[i][j]);
+          acc[i][j] = fmaf(a[i].z, b[j].z, acc[i][j]);
+          acc[i][j] = fmaf(a[i].w, b[j].w, acc[i][j]);
+        }
     }
-    __syncthreads();
+    __syncthreads();  // all are done with this stage before the copies after the next are requested into it
   }
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int m = m0 + tm + i;
+  for (int i = 0; i < 8; ++i) {
+    const int m = m0 + tm + 16 * i;
     if (m >= M) continue;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int n = n0 + tn + j;
+    for (int j = 0; j < 8; ++j) {
+      const int n = n0 + tn + 16 * j;
       if (n < N) out[(size_t)m * ldo + n] = acc[i][j] + (bias ? bias[n] : 0.f);
     }
   }
@@ -66,16 +113,10 @@ gemm_f32_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ 
 // The same sums for up to 16 rows (decoding), laid out for streaming the weights: a block of 128 threads takes 8
 // weight rows, thread (n, m) owns out[m][n] and adds its products for k = 0..K-1 in ascending order, exactly as
 // the kernel above does, so a row's result is the same bit for bit whichever of the two computed it.  With 8
-// weight rows per block a matrix of 896 rows is spread over 112 blocks (the kernel above would use 14).
+// weight rows per block a matrix of 896 rows is spread over 112 blocks (the kernel above would use 7).
 #define G32S_ROWS 16
 #define G32S_COLS 8
 #define G32S_KT 128
-
-// Four bytes from global to shared memory without passing through registers; `valid` false: a zero instead.
-__device__ __forceinline__ void g32_cp_async4(float* smem, const float* gmem, bool valid) {
-  const int n = valid ? 4 : 0;
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem), "r"(n));
-}
 
 __global__ void __launch_bounds__(G32S_ROWS * G32S_COLS)
 gemm_f32_small_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ w, const float* __restrict__ bias,
@@ -139,7 +180,11 @@ MS_API int ms_gemm_f32(const float* x, int ldx, const float* w, const float* bia
   }
   dim3 grid((N + G32_BN - 1) / G32_BN, (M + G32_BM - 1) / G32_BM);
   MS_REQUIRE(grid.y <= 65535, "gemm_f32: %d rows are more than one launch takes", M);
-  gemm_f32_kernel<<<grid, 256, 0, stream>>>(x, ldx, w, bias, out, ldo, M, N, K);
+  const bool vec = K % 4 == 0 && ldx % 4 == 0 && ((uintptr_t)x | (uintptr_t)w) % 16 == 0;
+  if (vec)
+    gemm_f32_kernel<true><<<grid, 256, 0, stream>>>(x, ldx, w, bias, out, ldo, M, N, K);
+  else
+    gemm_f32_kernel<false><<<grid, 256, 0, stream>>>(x, ldx, w, bias, out, ldo, M, N, K);
   MS_LAUNCH_CHECK("gemm_f32");
   return 0;
 }

@@ -70,7 +70,7 @@ class _Signatures:
     ms_add_bias = [P, I, P, I, I, I, P]
     ms_silu_mul = [P, P, I, I, I, P]
     ms_rope_kv_store = [P, I, I, P, P, P, P, I, I, P, I, I, P, P, P, I, I, I, I, I, I, P]
-    ms_attention_generic = [P, P, P, P, I, I, P, P, P, I, I, I, I, I, I, I, I, F, P]
+    ms_attention_generic = [P, P, P, P, I, I, P, P, P, I, I, I, I, I, I, I, I, F, I, P]
     ms_gemm_f32 = [P, I, P, P, P, I, I, I, I, P]
     ms_attention_decode = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P]
     ms_attention_decode_cluster = [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, I, I, P]
@@ -296,8 +296,11 @@ def attention_generic(
     head_dim: int,
     window: Optional[int],
     scale: float,
+    share_rows: bool = False,
 ) -> torch.Tensor:
-    """The exact paged attention kernel.  q, out [T, Hq*hd]; pages [num_pages, Hkv, page, hd]."""
+    """The exact paged attention kernel.  q, out [T, Hq*hd]; pages [num_pages, Hkv, page, hd].  `share_rows`: rows that
+    follow one another in a sequence (portions of prompts) share the tiles of keys they read, eight rows a block; the
+    results are the same bits either way."""
     tokens = q.shape[0]
     _need(q.is_contiguous() and out.is_contiguous() and q.dtype == out.dtype, "attention: bad layout")
     _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == v_pages.dtype, "attention: bad pages")
@@ -307,7 +310,7 @@ def attention_generic(
         lib().ms_attention_generic(
             _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _code(q), _code(k_pages), _ptr(positions),
             _ptr(seq_of_token), _ptr(block_table), block_table.shape[1], k_pages.shape[0], tokens, num_heads,
-            num_kv_heads, head_dim, k_pages.shape[2], int(window or 0), float(scale), _stream(),
+            num_kv_heads, head_dim, k_pages.shape[2], int(window or 0), float(scale), 1 if share_rows else 0, _stream(),
         ),
         "attention_generic",
     )

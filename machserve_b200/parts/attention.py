@@ -281,7 +281,7 @@ class Attention(Mixer):
         if not self.fast:
             return ops.attention_generic(
                 q, cache.k_pages, cache.v_pages, out, ctx.positions, ctx.slot_of_token, cache.block_table(ctx),
-                self.hq, self.hkv, self.hd, self.window, self.scale,
+                self.hq, self.hkv, self.hd, self.window, self.scale, share_rows=ctx.max_query_len > 1,
             )
         table = cache.block_table(ctx)
         work = ctx.work[self.PLAN]

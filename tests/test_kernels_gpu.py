@@ -277,6 +277,32 @@ def test_attention_generic(lens, hq, hkv, hd, page, window, dtype):
 
 
 @pytest.mark.parametrize("lens,hq,hkv,hd,page,window", ATT_CASES)
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_generic_rows_that_share_tiles(lens, hq, hkv, hd, page, window, dtype):
+    """Portions of prompts (runs of consecutive rows, cut anywhere, next to single rows of other sequences): eight rows
+    a block share the tiles they read, and every row comes out with the same bits as when it is computed alone."""
+    import torch
+    from machserve_b200 import ops
+    case = PagedCase(lens, hq, hkv, hd, page, window, dtype=dtype)
+    rows = []
+    for s, n in enumerate(lens):
+        if s % 3 == 2:
+            rows += [(s, n - 1)]                                # a single row
+        else:
+            a = max(0, n - 45) if s % 2 else 0                  # a portion at the end of a sequence, or from its start
+            rows += [(s, p) for p in range(a, min(n, a + 77))]  # (no multiple of eight rows, and across tiles of 32 keys)
+    q, want, pos, slot = case.queries(rows)
+    alone = torch.empty((len(rows), hq * hd), dtype=case.tdtype, device=dev())
+    ops.attention_generic(T(q, case.tdtype), case.k_pages, case.v_pages, alone, pos, slot, case.table, hq, hkv, hd, window, hd ** -0.5)
+    shared = torch.full((len(rows), hq * hd), 7.0, dtype=case.tdtype, device=dev())
+    ops.attention_generic(T(q, case.tdtype), case.k_pages, case.v_pages, shared, pos, slot, case.table, hq, hkv, hd, window, hd ** -0.5,
+                          share_rows=True)
+    tol = 2e-6 if dtype == "float32" else 2.0 ** -8
+    assert np.abs(N(shared) - want).max() <= tol * max(1.0, np.abs(want).max()) + 1e-6
+    assert torch.equal(shared.view(torch.int32 if dtype == "float32" else torch.int16), alone.view(torch.int32 if dtype == "float32" else torch.int16))
+
+
+@pytest.mark.parametrize("lens,hq,hkv,hd,page,window", ATT_CASES)
 @pytest.mark.parametrize("splits", [1, 2, 5])
 def test_attention_decode(lens, hq, hkv, hd, page, window, splits):
     import torch
