@@ -151,9 +151,11 @@ attention_generic_kernel(const TA* __restrict__ q, const TC* __restrict__ k_page
 // once for R rows instead of once for each; row by row, each warp does exactly what it does in the kernel above (its
 // tiles, its order of sums, the merge in warp order), so a row's result is the same bit for bit whichever kernel
 // computed it and whatever rows stood beside it.  NACC: head_dim / 32 rounded up.
+// HEADS: the R "rows" of a block are instead up to R query heads of ONE token that share a key head (decoding with
+// grouped queries): they read the same keys and values, which one block then stages once for all of them.
 #define ATT_ROWS 8
 
-template <typename TA, typename TC, int ATT_WARPS, int NACC>
+template <typename TA, typename TC, int ATT_WARPS, int NACC, bool HEADS>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 attention_generic_rows_kernel(const TA* __restrict__ q, const TC* __restrict__ k_pages, const TC* __restrict__ v_pages,
                               TA* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
@@ -165,9 +167,22 @@ attention_generic_rows_kernel(const TA* __restrict__ q, const TC* __restrict__ k
   float* k_all = q_s + ATT_ROWS * hd;
   float* v_all = k_all + (size_t)ATT_WARPS * 32 * (hd + 1);
   float* part = v_all + (size_t)ATT_WARPS * 32 * hd;
-  const int group = blockIdx.x / hq, h = blockIdx.x - group * hq;
-  const int t0 = group * ATT_ROWS;
-  const int kvh = h / (hq / hkv);
+  // row r of the block is (token tok0 + r * tok_step, head head0 + r * head_step), if r < live_rows
+  const int groups = hq / hkv;
+  int tok0, tok_step, head0, head_step, live_rows, kvh;
+  if (HEADS) {
+    const int per_kv = (groups + ATT_ROWS - 1) / ATT_ROWS;
+    const int t = blockIdx.x / (hkv * per_kv), rem = blockIdx.x - t * (hkv * per_kv);
+    kvh = rem / per_kv;
+    const int g0 = (rem - kvh * per_kv) * ATT_ROWS;
+    tok0 = t; tok_step = 0; head0 = kvh * groups + g0; head_step = 1;
+    live_rows = min(ATT_ROWS, groups - g0);
+  } else {
+    const int group = blockIdx.x / hq, h = blockIdx.x - group * hq;
+    kvh = h / groups;
+    tok0 = group * ATT_ROWS; tok_step = 1; head0 = h; head_step = 0;
+    live_rows = min(ATT_ROWS, tokens - tok0);
+  }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const size_t head_off = (size_t)kvh * page_size * hd;
   const size_t page_elems = (size_t)hkv * page_size * hd;
@@ -177,14 +192,13 @@ attention_generic_rows_kernel(const TA* __restrict__ q, const TC* __restrict__ k
   int seq[ATT_ROWS], pos[ATT_ROWS], first[ATT_ROWS];
 #pragma unroll
   for (int r = 0; r < ATT_ROWS; ++r) {
-    const int t = t0 + r;
-    seq[r] = t < tokens ? seq_of_token[t] : -1;
-    pos[r] = seq[r] >= 0 ? positions[t] : -1;
+    seq[r] = r < live_rows ? seq_of_token[tok0 + r * tok_step] : -1;
+    pos[r] = seq[r] >= 0 ? positions[tok0 + r * tok_step] : -1;
     first[r] = (window > 0 && pos[r] - window + 1 > 0) ? pos[r] - window + 1 : 0;
   }
   for (int e = threadIdx.x; e < ATT_ROWS * hd; e += blockDim.x) {
     const int r = e / hd, d = e - r * hd;
-    q_s[e] = t0 + r < tokens ? ms_to_float(q[((size_t)(t0 + r) * hq + h) * hd + d]) : 0.f;
+    q_s[e] = r < live_rows ? ms_to_float(q[((size_t)(tok0 + r * tok_step) * hq + head0 + r * head_step) * hd + d]) : 0.f;
   }
   __syncthreads();
 
@@ -331,8 +345,8 @@ attention_generic_rows_kernel(const TA* __restrict__ q, const TC* __restrict__ k
   }
   __syncthreads();
   for (int r = warp; r < ATT_ROWS; r += ATT_WARPS) {
-    const int t = t0 + r;
-    if (t >= tokens || seq_of_token[t] < 0) continue;
+    const int t = tok0 + r * tok_step, h = head0 + r * head_step;
+    if (r >= live_rows || seq_of_token[t] < 0) continue;
     float mm = -INFINITY;
     for (int w = 0; w < ATT_WARPS; ++w) mm = fmaxf(mm, part[((size_t)w * ATT_ROWS + r) * pw + hd]);
     float f[ATT_WARPS], ll = 0.f;
@@ -352,7 +366,7 @@ attention_generic_rows_kernel(const TA* __restrict__ q, const TC* __restrict__ k
 
 // q, out: [tokens, hq*hd].  window <= 0: every earlier key is visible.  share_rows: the step has rows that follow one
 // another in a sequence (portions of prompts): eight rows a block share the tiles they read (head sizes up to 128);
-// the results are the same bits either way.
+// else the query heads of a token that share a key head do.  The results are the same bits either way.
 MS_API int ms_attention_generic(const void* q, const void* k_pages, const void* v_pages, void* out, int act_dtype,
                                 int cache_dtype, const int* positions, const int* seq_of_token,
                                 const int* block_table, int max_pages, int num_pages, int tokens, int hq, int hkv,
@@ -361,8 +375,12 @@ MS_API int ms_attention_generic(const void* q, const void* k_pages, const void* 
   MS_REQUIRE(tokens > 0 && hq > 0 && hkv > 0 && hq % hkv == 0, "attention: bad head counts hq=%d hkv=%d", hq, hkv);
   MS_REQUIRE(hd > 0 && hd <= ATT_MAX_HD, "attention: head_dim %d is outside (0, %d]", hd, ATT_MAX_HD);
   MS_REQUIRE(page_size > 0 && max_pages > 0 && num_pages > 0, "attention: bad cache sizes");
-  const bool rows = share_rows && hd <= 128 && tokens > 1;
-  const unsigned blocks = rows ? (unsigned)((tokens + ATT_ROWS - 1) / ATT_ROWS) * (unsigned)hq : (unsigned)tokens * (unsigned)hq;
+  const int groups = hq / hkv;
+  const bool rows = share_rows && hd <= 128 && tokens > 1;      // rows of portions share their tiles
+  const bool heads = !rows && hd <= 128 && groups > 1;          // the heads of a group share theirs
+  const unsigned blocks = rows    ? (unsigned)((tokens + ATT_ROWS - 1) / ATT_ROWS) * (unsigned)hq
+                          : heads ? (unsigned)tokens * (unsigned)hkv * (unsigned)((groups + ATT_ROWS - 1) / ATT_ROWS)
+                                  : (unsigned)tokens * (unsigned)hq;
 #define MS_ATT_SET_SMEM(KERN, BYTES)                                                                            \
   do {                                                                                                          \
     static size_t configured = 0;                                                                               \
@@ -380,24 +398,28 @@ MS_API int ms_attention_generic(const void* q, const void* k_pages, const void* 
     kern<<<blocks, (W) * 32, smem, stream>>>((const TA*)q, (const TC*)k_pages, (const TC*)v_pages, (TA*)out, positions, \
                                             seq_of_token, block_table, max_pages, num_pages, hq, hkv, hd, page_size, window, scale); \
   } while (0)
-#define MS_ATT_LAUNCH_ROWS(TA, TC, W, NACC)                                                                     \
+#define MS_ATT_LAUNCH_ROWS(TA, TC, W, NACC, H)                                                                   \
   do {                                                                                                          \
     const size_t smem = ((size_t)ATT_ROWS * hd + (size_t)(W) * 32 * (2 * hd + 1) + (size_t)(W) * ATT_ROWS * (hd + 2)) * sizeof(float); \
-    auto kern = attention_generic_rows_kernel<TA, TC, W, NACC>;                                                 \
+    auto kern = attention_generic_rows_kernel<TA, TC, W, NACC, H>;                                              \
     MS_ATT_SET_SMEM(kern, smem);                                                                                \
     kern<<<blocks, (W) * 32, smem, stream>>>((const TA*)q, (const TC*)k_pages, (const TC*)v_pages, (TA*)out, positions, \
                                             seq_of_token, block_table, max_pages, num_pages, tokens, hq, hkv, hd, page_size, window, scale); \
   } while (0)
-#define MS_ATT_CASE(TA, TC)                           \
-  do {                                                \
-    if (rows && hd <= 64)                             \
-      MS_ATT_LAUNCH_ROWS(TA, TC, ATT_MAX_WARPS, 2);   \
-    else if (rows)                                    \
-      MS_ATT_LAUNCH_ROWS(TA, TC, 4, 4);               \
-    else if (hd <= 64)                                \
-      MS_ATT_LAUNCH(TA, TC, ATT_MAX_WARPS);           \
-    else                                              \
-      MS_ATT_LAUNCH(TA, TC, 4);                       \
+#define MS_ATT_CASE(TA, TC)                                \
+  do {                                                     \
+    if (rows && hd <= 64)                                  \
+      MS_ATT_LAUNCH_ROWS(TA, TC, ATT_MAX_WARPS, 2, false); \
+    else if (rows)                                         \
+      MS_ATT_LAUNCH_ROWS(TA, TC, 4, 4, false);             \
+    else if (heads && hd <= 64)                            \
+      MS_ATT_LAUNCH_ROWS(TA, TC, ATT_MAX_WARPS, 2, true);  \
+    else if (heads)                                        \
+      MS_ATT_LAUNCH_ROWS(TA, TC, 4, 4, true);              \
+    else if (hd <= 64)                                     \
+      MS_ATT_LAUNCH(TA, TC, ATT_MAX_WARPS);                \
+    else                                                   \
+      MS_ATT_LAUNCH(TA, TC, 4);                            \
   } while (0)
   if (act_dtype == MS_F32 && cache_dtype == MS_F32)
     MS_ATT_CASE(float, float);
