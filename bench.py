@@ -455,8 +455,9 @@ def workload_fp32(a, pk, raw, layers):
 
 def workload_serving(a, pk):
     """Qwen2.5-1.5B sizes: 64 requests, prompts of 128 to 2,048 tokens (seeded), 256 new tokens each, through `Engine`
-    with its default budget of prompt tokens per step.  All requests arrive at time zero.  The same load runs once
-    untimed first (other token ids), which loads kernels and captures the steps that repeat."""
+    with its default budget of prompt tokens per step.  All requests arrive at time zero.  Three loads of other prompt
+    lengths and token ids run untimed first, as a server that has been up for a while: they load the kernels and
+    capture the graphs of the step sizes that keep coming (the timed load's own steps have not been seen before)."""
     import numpy as np
     import torch
 
@@ -472,11 +473,10 @@ def workload_serving(a, pk):
     runner = ModelRunner.from_random(config_from_json(cfg), seed=0, on_device=True, dtype="bf16", page_size=PAGE,
                                      num_pages=n_req * (-(-max_seq // PAGE)), max_requests=n_req,
                                      max_step_tokens=n_req + prefill_rows, max_seq_len=max_seq)
-    rng = np.random.default_rng(1)
-    lengths = [int(x) for x in rng.integers(lo, hi + 1, size=n_req)]
     wb, kvb = weight_bytes(raw, layers), kv_bytes_per_token(raw, layers)
 
-    def run(seed):
+    def run(seed, lengths_seed=1):
+        lengths = [int(x) for x in np.random.default_rng(lengths_seed).integers(lo, hi + 1, size=n_req)]
         eng = Engine(runner=runner, prefill_rows=prefill_rows)
         ids_rng = np.random.default_rng(seed)
         plans = []
@@ -505,11 +505,11 @@ def workload_serving(a, pk):
         made = sum(len(eng.generated(s)) for s in sids)
         for s in sids:
             eng.ack(s)
-        return wall, made, first, steps, plans, eng.counters
+        return wall, made, first, steps, plans, eng.counters, lengths
 
-    run(2)  # twice untimed: a shape is captured when it has come three times
-    run(2)
-    wall, made, first, steps, plans, counters = run(3)
+    for warm in range(3):
+        run(2, 100 + warm)
+    wall, made, first, steps, plans, counters, lengths = run(3)
     runner.check_device_status()
     # what the steps as planned have to read and to compute: the slower of the two bounds, step by step
     floor = 0.0
@@ -532,6 +532,7 @@ def workload_serving(a, pk):
         "ttft_ms_median": round(statistics.median(ttft_ms), 1), "ttft_ms_p95": round(p95(ttft_ms), 1),
         "ttft_steps_median": statistics.median(ttft_steps), "ttft_steps_p95": p95(ttft_steps),
         "roofline_floor_s": round(floor, 4), "roofline_frac": round(floor / wall, 4),
+        "graphs_of_decoding_steps": runner.graph_counts()["decode"], "graphs_of_other_steps": runner.graph_counts()["shapes"],
         "timing": "wall clock around the whole load through Engine.step, host ids in, sampled ids read by the host",
     })
     del runner

@@ -134,7 +134,7 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
   const int kvh = blockIdx.y, split = blockIdx.z;
   const int groups = hq / hkv;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int slot = slot_of_token[t];
+  const int slot = t >= 0 ? slot_of_token[t] : -1;  // (a list of rows may be padded with -1)
   const bool live = slot >= 0;  // a padding row still takes part in the cluster's barriers
   const int pos = live ? positions[t] : 0;
   const int first_key = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;

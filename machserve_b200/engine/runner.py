@@ -166,7 +166,10 @@ class ModelRunner:
         pad = 1
         while pad < max_requests:
             pad *= 2
-        rows, seqs = max(max_step_tokens, pad), pad
+        # (a step of any shape that is to be replayed from a graph is padded to a multiple of ROW_BUCKET rows and of
+        # SEQ_BUCKET sequences)
+        rows = max(-(-max_step_tokens // self.ROW_BUCKET) * self.ROW_BUCKET, pad)
+        seqs = max(pad, max_requests + self.SEQ_BUCKET)
         self._stage_len = 6 * rows + 4 * seqs + 1 + sum(p.plan_words(rows, seqs) for p in self._planners.values()) + 16
         self._pinned = [torch.empty(self._stage_len, dtype=torch.int32).pin_memory() for _ in range(3)]
         self._pinned_events: List[Optional[torch.cuda.Event]] = [None] * len(self._pinned)
@@ -188,6 +191,7 @@ class ModelRunner:
         self._shape_graphs: Dict[tuple, Tuple[torch.cuda.CUDAGraph, torch.Tensor, int]] = {}
         self._shape_seen: Dict[tuple, int] = {}
         self._decode_plan_cache: Dict[Tuple[int, int], tuple] = {}
+        self._capture_stream: Optional[torch.cuda.Stream] = None
 
     # ---------------------------------------------------------------- builders
 
@@ -371,8 +375,14 @@ class ModelRunner:
             decode_only=max_q == 1,
         )
 
-    def _stage(self, entries: Sequence[StepEntry]) -> StepContext:
-        """Fills one pinned buffer with the step's index arrays and copies it to the device in one transfer."""
+    ROW_BUCKET, SEQ_BUCKET, WANT_BUCKET = 64, 16, 16
+
+    def _stage(self, entries: Sequence[StepEntry], bucketed: bool = False) -> StepContext:
+        """Fills one pinned buffer with the step's index arrays and copies it to the device in one transfer.
+        `bucketed`: the step is padded to 16, 32 or a multiple of ROW_BUCKET rows by rows that belong to no sequence and
+        no request (no slot, no pages: every kernel passes them over), its sequences to a multiple of SEQ_BUCKET by
+        sequences without rows, its wanted rows to WANT_BUCKET or a power of two by repeats of the last one, and the
+        parts pad their lists: steps of like size then have the same lengths everywhere and can share a captured graph."""
         turn = self._pinned_turn()
         host = self._pinned[turn].numpy()
         counts = [len(e.tokens) for e in entries]
@@ -383,8 +393,15 @@ class ModelRunner:
         for n in counts:
             row0.append(row)
             row += n
-        plans, plan_sizes = self._plans(StepShape(T, S, row0, counts, starts))
-        views, total = self._layout(T, S, W, plan_sizes)
+        extra = 0
+        if bucketed:  # 16 rows (the few-row kernels' limit), 32, then multiples of ROW_BUCKET
+            extra = (16 if T <= 16 else 32 if T <= 32 else -(-T // self.ROW_BUCKET) * self.ROW_BUCKET) - T
+        empty = -S % self.SEQ_BUCKET if bucketed else 0
+        Tp, Sp = T + extra, S + empty
+        Wp = min(max(self.WANT_BUCKET, 1 << (W - 1).bit_length()), Tp) if bucketed and W else W
+        shape = StepShape(Tp, Sp, row0 + [T] * empty, counts + [0] * empty, starts + [0] * empty, bucketed)
+        plans, plan_sizes = self._plans(shape)
+        views, total = self._layout(Tp, Sp, Wp, plan_sizes)
         h = {name: host[a : a + n] for name, (a, n) in views.items()}
         tok, pos, seq, slot = h["token_ids"], h["positions"], h["seq_of_token"], h["slot_of_token"]
         cu, start, length, slots, want = h["cu_tokens"], h["seq_start"], h["seq_len"], h["state_slots"], h["want_rows"]
@@ -403,13 +420,21 @@ class ModelRunner:
                 want[w] = row + int(k)
                 w += 1
             cu[i + 1] = row + n
+        if extra:  # rows of no sequence
+            tok[T:], pos[T:], seq[T:], slot[T:] = 0, 0, -1, -1
+            h["from_sampled"][T:] = -1
+        if empty:  # sequences of no rows
+            start[S:], length[S:], slots[S:] = 0, 0, 0
+            cu[S + 1 :] = T
+        if Wp > W:
+            want[W:] = want[W - 1]
         for key, plan in plans:
             for name, lst in plan.lists.items():
                 h[(key, name)][:] = lst
         self._send(turn, total, views, entries)
         max_q = max(counts)
         max_len = max(p + n for p, n in zip(starts, counts))
-        return self._context(views, T, S, W, plans, max_q, max_len, cu, start, slots)
+        return self._context(views, Tp, Sp, Wp, plans, max_q, max_len, cu, start, slots)
 
     # ------------------------------------------------------- decoding with graphs
 
@@ -458,6 +483,25 @@ class ModelRunner:
         self._send(turn, total, views, entries)
         return views, plans
 
+    def _capture(self, forward):
+        """Records the launches of `forward()` in a CUDA graph (they do not run).  On a stream of its own, ordered after
+        and before the current one; without the pause for the collector and the return of cached memory that
+        torch.cuda.graph() makes, which cost tens of milliseconds: the scratch memory has its size by now, and what a
+        forward pass allocates beside it is small and stays with the graph."""
+        if self._capture_stream is None:
+            self._capture_stream = torch.cuda.Stream(device=self.device)
+        main, side = torch.cuda.current_stream(), self._capture_stream
+        side.wait_stream(main)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            graph.capture_begin()
+            try:
+                out = forward()
+            finally:
+                graph.capture_end()
+        main.wait_stream(side)
+        return graph, out
+
     def _decode_with_graph(self, entries: Sequence[StepEntry], b: int, length: int) -> torch.Tensor:
         views, plans = self._stage_decode(entries, b, length)
         key = (b, length)
@@ -466,9 +510,7 @@ class ModelRunner:
             self.model.forward(ctx, self.bindings)  # sizes the scratch memory and loads every kernel
             torch.cuda.current_stream().synchronize()
             before = ops.launches()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                logits = self.model.forward(ctx, self.bindings)
+            graph, logits = self._capture(lambda: self.model.forward(ctx, self.bindings))
             self._graphs[key] = (graph, logits, ops.launches() - before)
         graph, logits, launches = self._graphs[key]
         graph.replay()
@@ -505,40 +547,44 @@ class ModelRunner:
         self.steps += 1
         return logits
 
-    MAX_SHAPE_GRAPHS = 24
-    CAPTURE_AFTER = 3  # a capture costs as much as some tens of such steps run plainly: only shapes that keep coming
+    MAX_SHAPE_GRAPHS = 160
+    CAPTURE_AFTER = 1  # a capture costs as much as one or two such steps run plainly: a shape that comes again is captured
 
     def _step_general(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        """A step of any shape.  A shape that keeps coming (the same numbers of rows, sequences and wanted rows and the
-        same work lists: a server's steady portions, a benchmark's prompt) is captured in a CUDA graph at its fourth
-        occurrence and replayed from then on: the index arrays lie at the same places of the staging buffer, only
-        their contents change."""
-        ctx = self._stage(entries)
+        """A step of any shape.  With graphs, the step is padded so that steps of like size (rows up to the same
+        multiple of ROW_BUCKET, tiles of portions, contexts of the same class) have the same lengths everywhere; such
+        a shape is captured in a CUDA graph when it has come CAPTURE_AFTER times and replayed from then on: the index
+        arrays lie at the same places of the staging buffer, only their contents change.  A server's steady mix of
+        a portion of a prompt beside decoded tokens, and a benchmark's prompt, come to a few dozen shapes."""
         if not self.use_graphs:
-            return self.model.forward(ctx, self.bindings)
-        key = (ctx.num_tokens, ctx.num_seqs, ctx.num_wanted,
+            return self.model.forward(self._stage(entries), self.bindings)
+        wanted = sum(len(e.want) for e in entries)
+        ctx = self._stage(entries, bucketed=True)
+        key = (ctx.num_tokens, ctx.num_seqs, ctx.num_wanted, ctx.max_query_len > 1,
                tuple((k, tuple(w.sizes.values()), w.shape) for k, w in ctx.work.items()))
         hit = self._shape_graphs.get(key)
         if hit is not None:
             graph, logits, launches = hit
             graph.replay()
             ops.count_launches(launches)
-            return logits
+            return logits[:wanted]
         seen = self._shape_seen.get(key, 0)
         self._shape_seen[key] = seen + 1
         if seen < self.CAPTURE_AFTER or len(self._shape_graphs) >= self.MAX_SHAPE_GRAPHS:
             if len(self._shape_seen) > 4096:
                 self._shape_seen.clear()
-            return self.model.forward(ctx, self.bindings)
+            return self.model.forward(ctx, self.bindings)[:wanted]
         # the scratch memory has its size and every kernel has been loaded by the runs before
         before = ops.launches()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            logits = self.model.forward(ctx, self.bindings)
+        graph, logits = self._capture(lambda: self.model.forward(ctx, self.bindings))
         self._shape_graphs[key] = (graph, logits, ops.launches() - before)
         graph.replay()
         ops.count_launches(ops.launches() - before)
-        return logits
+        return logits[:wanted]
+
+    def graph_counts(self) -> Dict[str, int]:
+        """How many captured graphs the runner holds: of decoding steps, and of steps of other shapes."""
+        return {"decode": len(self._graphs), "shapes": len(self._shape_graphs)}
 
     def check_device_status(self) -> None:
         """Raises if a tensor-core kernel gave up one of its bounded waits since the last check (synchronizes)."""

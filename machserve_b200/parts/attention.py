@@ -107,7 +107,7 @@ class Attention(Mixer):
         return self.PLAN
 
     def plan_words(self, max_rows, max_seqs):
-        return max_seqs + 2 * (max_rows // self.TILE + max_seqs) + 2 * (max_rows // self.BIG_TILE + max_seqs)
+        return max_seqs + 2 * (max_rows // self.TILE + max_seqs + 4) + 2 * (max_rows // self.BIG_TILE + max_seqs + 2)
 
     def plan(self, step):
         """Rows that are alone in their sequence (decoding) go to the kernel that splits a row's keys over blocks;
@@ -116,6 +116,8 @@ class Attention(Mixer):
         longest = longest_portion = 0  # the most keys a decoding row sees, and a row of a portion
         key_tiles = 0                  # tiles of 128 keys that the tiles of 128 rows see, in all
         for row, n, start in zip(step.row0, step.count, step.start):
+            if n == 0:
+                continue  # a sequence without rows (padding of a step to a fixed number of sequences)
             if n == 1:
                 single.append(row)
                 longest = max(longest, start + 1)
@@ -130,12 +132,22 @@ class Attention(Mixer):
                     bn.append(rows)
                     first = max(0, start + a - self.window + 1) if self.window else 0
                     key_tiles += (start + a + rows - 1) // self.BIG_TILE - first // self.BIG_TILE + 1
-        lists = {"single_rows": single, "tile_row0": t0, "tile_rows": tn, "big_tile_row0": b0, "big_tile_rows": bn}
         # what the launches depend on beside the lengths of the lists, in coarse steps (a step is replayed from a graph
         # under these): the longest context of a decoding row, of a portion's row, and the mean number of key tiles
         # that a tile of a portion's rows sees
-        mean_key_tiles = -(-key_tiles // (2 * len(b0))) * 2 if b0 else 0
-        return WorkPlan(lists, (-(-longest // self.CONTEXT_BUCKET), -(-longest_portion // self.CONTEXT_BUCKET), mean_key_tiles))
+        classes = [-(-longest // self.CONTEXT_BUCKET), -(-longest_portion // self.CONTEXT_BUCKET),
+                   -(-key_tiles // (2 * len(b0))) * 2 if b0 else 0]
+        if step.bucketed:
+            # a graph for all steps of like size: lists of a few lengths (a tile of no rows does nothing), and the
+            # three numbers rounded up to powers of two (they are upper bounds to the kernels' launch rules)
+            for rows0, rows_n, multiple in ((t0, tn, 4), (b0, bn, 2)):
+                pad = -len(rows0) % multiple
+                rows0 += [0] * pad
+                rows_n += [0] * pad
+            single += [-1] * (-len(single) % 16)  # (no row: the blocks of such an entry do nothing)
+            classes = [1 << (c - 1).bit_length() if c > 0 else 0 for c in classes]
+        lists = {"single_rows": single, "tile_row0": t0, "tile_rows": tn, "big_tile_row0": b0, "big_tile_rows": bn}
+        return WorkPlan(lists, tuple(classes))
 
     # -- with few rows in bfloat16: the norm in front and the add behind inside the products -------------------------
     fused_rows = 16

@@ -167,13 +167,18 @@ def as_delta(pending):
 class StepShape:
     """The rows of one step as the host knows them: what `Part.plan` makes its work lists from.
     Sequence i brings rows [row0[i], row0[i] + count[i]) at positions start[i], start[i] + 1, ...
-    A step that is padded to a fixed size ends with sequences of one row that belong to no request."""
+    A decoding step that is padded to a fixed size ends with sequences of one row that belong to no request.
+    `bucketed`: the step is to be replayed from a graph that is shared by all steps of like size.  It may then end
+    with sequences of no rows, and `rows` may count rows behind the last sequence's that belong to no sequence (their
+    slot and sequence numbers are -1); a plan should pad its lists with entries that do nothing and give its `shape`
+    in coarse classes, so that few different (lengths, shape) come out of the many steps of a serving load."""
 
     rows: int
     seqs: int
     row0: Sequence[int]
     count: Sequence[int]
     start: Sequence[int]
+    bucketed: bool = False
 
 
 @dataclass
