@@ -578,6 +578,9 @@ def workload_mixed(a, pk):
         entries = [StepEntry(("p", r), ids(portion), [portion - 1]) for r in range(n_pf)]
         entries += [StepEntry(("d", r), ids(1), [0]) for r in range(n_dec)]
         torch.cuda.synchronize()
+        bracket = a.profile == "mixed" and rep == reps + 3
+        if bracket:
+            torch.cuda.cudart().cudaProfilerStart()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0 = time.perf_counter()
         e0.record()
@@ -585,7 +588,9 @@ def workload_mixed(a, pk):
         toks, _ = sampler.sample(logits, greedy, states)
         e1.record()
         torch.cuda.synchronize()
-        if rep >= 4:  # the first passes load kernels and size the scratch memory, the fourth captures the step
+        if bracket:
+            torch.cuda.cudart().cudaProfilerStop()
+        if rep >= 4:  # the first passes load kernels and size the scratch memory, the second captures the step
             walls.append((time.perf_counter() - t0) * 1000)
             times.append(e0.elapsed_time(e1))
         assert len(toks) == n_dec + n_pf
@@ -631,7 +636,7 @@ def main() -> int:
     ap.add_argument("--only", default="headline,fp32,serving_1p5b,mixed_7b",
                     help="which parts to run: headline, fp32, serving_1p5b, mixed_7b (comma separated)")
     ap.add_argument("--no-points", action="store_true", help="skip the further batch sizes and the prefill")
-    ap.add_argument("--profile", default=None, choices=["decode", "prefill"],
+    ap.add_argument("--profile", default=None, choices=["decode", "prefill", "mixed"],
                     help="which timed region is bracketed by cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     ap.add_argument("--kernel", default=None, choices=["attention_prefill", "gemm"],
                     help="time one kernel alone at the configuration's head sizes instead of the step, and print its own line")

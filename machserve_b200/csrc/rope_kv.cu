@@ -93,28 +93,44 @@ __global__ void rope_kv_store_vec_kernel(const __nv_bfloat16* __restrict__ qkv, 
                                          __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages, int hq,
                                          int hkv, int hd, int page_size) {
   ms_pdl_trigger();
-  ms_pdl_wait();
   const int t = blockIdx.x;
-  const int seq = seq_of_token[t];
-  if (seq < 0) return;
-  const int pos = positions[t];
-  const __nv_bfloat16* row = qkv + (size_t)t * ld;
   const int half = hd / 2, per_head = half / 8;
   const int qw = hq * hd, kw = hkv * hd;
+  const int rot_items = (hq + hkv) * per_head, v_items = kw / 8;
+  // what does not depend on the kernel before: the row's sequence and position, its page, its angles
+  const int seq = seq_of_token[t];
+  const int pos = positions[t];
   size_t cache_base = 0;
-  bool store = hkv > 0;
+  bool store = hkv > 0 && seq >= 0;
   if (store) {
     const int page = block_table[(size_t)seq * max_pages + pos / page_size];
     store = page >= 0 && page < num_pages;
     cache_base = (size_t)(store ? page : 0) * hkv * page_size * hd + (size_t)(pos % page_size) * hd;
   }
+  ms_pdl_wait();
+  if (seq < 0) return;  // padding row
+  const __nv_bfloat16* row = qkv + (size_t)t * ld;
   const float2* cs = cos_sin + (size_t)pos * half;
-  const int rot_items = (hq + hkv) * per_head, v_items = kw / 8;
   for (int e = threadIdx.x; e < rot_items + v_items; e += blockDim.x) {
     if (e < rot_items) {
       const int head = e / per_head, j = (e - head * per_head) * 8;
       const int col = head * hd + j;
-      uint4 ua = *reinterpret_cast<const uint4*>(row + col), ub = *reinterpret_cast<const uint4*>(row + col + half);
+      // all loads of the item first (two of the row, four of the angles, four of the bias), then the arithmetic
+      const uint4 ua = *reinterpret_cast<const uint4*>(row + col), ub = *reinterpret_cast<const uint4*>(row + col + half);
+      float4 c[4], ba[2], bb[2];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) c[i] = *reinterpret_cast<const float4*>(cs + j + 2 * i);  // (cos, sin) of two pairs
+      if (bias) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          ba[i] = *reinterpret_cast<const float4*>(bias + col + 4 * i);
+          bb[i] = *reinterpret_cast<const float4*>(bias + col + half + 4 * i);
+        }
+      } else {
+        ba[0] = ba[1] = bb[0] = bb[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      const float* fa = reinterpret_cast<const float*>(ba);
+      const float* fb = reinterpret_cast<const float*>(bb);
       const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&ua);
       const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&ub);
       uint4 oa, ob;
@@ -123,13 +139,11 @@ __global__ void rope_kv_store_vec_kernel(const __nv_bfloat16* __restrict__ qkv, 
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         float2 a = __bfloat1622float2(ha[i]), b = __bfloat1622float2(hb[i]);
-        if (bias) {
-          a.x += bias[col + 2 * i];
-          a.y += bias[col + 2 * i + 1];
-          b.x += bias[col + half + 2 * i];
-          b.y += bias[col + half + 2 * i + 1];
-        }
-        const float2 c0 = cs[j + 2 * i], c1 = cs[j + 2 * i + 1];
+        a.x += fa[2 * i];
+        a.y += fa[2 * i + 1];
+        b.x += fb[2 * i];
+        b.y += fb[2 * i + 1];
+        const float2 c0 = make_float2(c[i].x, c[i].y), c1 = make_float2(c[i].z, c[i].w);
         pa[i] = __floats2bfloat162_rn(a.x * c0.x - b.x * c0.y, a.y * c1.x - b.y * c1.y);
         pb[i] = __floats2bfloat162_rn(a.x * c0.y + b.x * c0.x, a.y * c1.y + b.y * c1.x);
       }
@@ -145,17 +159,21 @@ __global__ void rope_kv_store_vec_kernel(const __nv_bfloat16* __restrict__ qkv, 
       const int c = (e - rot_items) * 8;
       const int kvh = c / hd, dd = c - kvh * hd;
       const uint4 u = *reinterpret_cast<const uint4*>(row + qw + kw + c);
+      float4 bv[2];
+      if (bias) {
+        bv[0] = *reinterpret_cast<const float4*>(bias + qw + kw + c);
+        bv[1] = *reinterpret_cast<const float4*>(bias + qw + kw + c + 4);
+      } else {
+        bv[0] = bv[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      const float* fv = reinterpret_cast<const float*>(bv);
       const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
       uint4 o;
       __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         float2 f = __bfloat1622float2(h[i]);
-        if (bias) {
-          f.x += bias[qw + kw + c + 2 * i];
-          f.y += bias[qw + kw + c + 2 * i + 1];
-        }
-        po[i] = __floats2bfloat162_rn(f.x, f.y);
+        po[i] = __floats2bfloat162_rn(f.x + fv[2 * i], f.y + fv[2 * i + 1]);
       }
       *reinterpret_cast<uint4*>(v_pages + cache_base + (size_t)kvh * page_size * hd + dd) = o;
     }
@@ -178,7 +196,7 @@ MS_API int ms_rope_kv_store(const void* qkv, int act_dtype, int ld, const float*
   MS_REQUIRE(hkv == 0 || (page_size > 0 && max_pages > 0 && num_pages > 0), "rope_kv_store: bad cache sizes");
   MS_REQUIRE(rot == 0 || cos_sin != nullptr, "rope_kv_store: rotation without a table");
   if (act_dtype == MS_BF16 && cache_dtype == MS_BF16 && rot == hd && !interleaved && hd % 16 == 0 && ld % 8 == 0 &&
-      ((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages) % 16 == 0) {
+      ((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)bias | (uintptr_t)cos_sin) % 16 == 0) {
     int items = (hq + hkv) * (hd / 16) + hkv * hd / 8;
     int vthreads = (items + 31) / 32 * 32;
     vthreads = vthreads > 256 ? 256 : vthreads;
