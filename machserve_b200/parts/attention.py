@@ -298,8 +298,25 @@ class Attention(Mixer):
         table = cache.block_table(ctx)
         work = ctx.work[self.PLAN]
         lists, sizes = work.lists, work.sizes
-        if sizes["single_rows"]:
+        # decoding rows beside portions of prompts: the two kernels read and write different rows, one waits for
+        # memory and one for the tensor cores.  In a captured step they run side by side, as two branches of the graph
+        # (when a step is launched plainly, the second stream's events would cost the host more than they save).
+        side = None
+        if sizes["single_rows"] and sizes["tile_row0"] and torch.cuda.is_current_stream_capturing():
+            main, side = torch.cuda.current_stream(), rt.side_stream()
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                self._attend_single(ctx, q, cache, out)
+        elif sizes["single_rows"]:
             self._attend_single(ctx, q, cache, out)
+        self._attend_portions(ctx, q, cache, out, table, work)
+        if side is not None:
+            main.wait_stream(side)
+        return out
+
+    def _attend_portions(self, ctx, q, cache, out, table, work):
+        """The rows of prompt portions, in tiles of rows."""
+        rt, lists, sizes = self.rt, work.lists, work.sizes
         if sizes["big_tile_row0"] and self.tc_prefill and cache.k_pages.shape[2] in self.tc_pages:
             # portions of prompts on the tcgen05 tensor cores, in tiles of up to 128 rows; with few tiles the keys of
             # each are split over several blocks (chosen from the longest portion's keys, by bucket)

@@ -138,10 +138,19 @@ class Runtime:
     workspace: Workspace
     max_positions: int
     sm_count: int = 148
+    _side: Optional["torch.cuda.Stream"] = None
 
     @property
     def is_f32(self) -> bool:
         return self.dtype == torch.float32
+
+    def side_stream(self) -> "torch.cuda.Stream":
+        """A second stream, for two launches of a part that do not depend on each other.  The part orders it behind
+        the current stream before and the current stream behind it after; in a captured step that becomes two
+        branches of the graph."""
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=self.device)
+        return self._side
 
 
 @dataclass
