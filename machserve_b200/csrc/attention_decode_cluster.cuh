@@ -36,6 +36,18 @@ struct DclRaw {
   int store;              // the row carries k and v of its position, to be written into the cache
 };
 
+// Few rows with long contexts: a (row, kv head) pair's keys go to `parts` clusters instead of one.  Each cluster
+// leaves its merged sums in `scratch` (per pair and part: groups * HD sums, then 16 maxima and 16 sums of a row's
+// probabilities) and counts itself in `counters` (one per pair: zero before the first launch, left zero by every
+// launch); the cluster that counts last merges the parts in their order, so the result does not depend on who
+// came last, and no cluster waits for another.
+struct DclOuter {
+  int parts;  // 1: the cluster writes the output itself
+  float* scratch;
+  int* counters;
+};
+#define DCL_MAX_PARTS 16
+
 // Requests `ntiles` tiles of 64 keys and their values, starting at tile `tile0`, into consecutive stages.  One
 // copy of this code serves the request before the wait and those of later rounds (the kernel's code is kept
 // small on purpose: a decoding step is a chain of short kernels, and each finds the instruction cache cold).
@@ -106,14 +118,14 @@ __device__ __forceinline__ void dcl_load_part(__nv_bfloat16* tile_s, const __nv_
 // tile each serve blocks with long runs of keys; four warps with half a tile each, blocks that can hold only two
 // tiles (many blocks on the GPU: more of them share an SM); eight warps with half a tile each, the few blocks of a
 // small batch, where a row's chain of dependent steps is what the step waits for.
-template <int HD, bool FUSED, int KPW, int DCL_WARPS>
+template <int HD, bool FUSED, int KPW, int DCL_WARPS, bool OUTER>
 __global__ void __launch_bounds__(DCL_WARPS * 32)
 attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw, __nv_bfloat16* k_pages,
                                 __nv_bfloat16* v_pages, __nv_bfloat16* __restrict__ out,
                                 const int* __restrict__ rows, const int* __restrict__ positions,
                                 const int* __restrict__ slot_of_token, const int* __restrict__ block_table,
                                 int max_pages, int num_pages, int hq, int hkv, int page_size, int window,
-                                float scale_log2, int num_splits, int stages) {
+                                float scale_log2, int num_splits, int stages, DclOuter outer) {
   constexpr int STRIDE = HD + 8;
   constexpr int TILE_ELEMS = DCL_TILE * STRIDE;
   constexpr int DCL_THREADS = DCL_WARPS * 32;
@@ -131,7 +143,12 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
   // everything up to the wait reads only what no kernel of this step writes: the step's index arrays,
   // the block tables, and keys and values of positions before the current one
   const int t = rows ? rows[blockIdx.x] : blockIdx.x;
-  const int kvh = blockIdx.y, split = blockIdx.z;
+  // blockIdx.z: the clusters of a pair one after the other (OUTER: more than one); `split` is the block's rank in its
+  // cluster (a power of two of blocks)
+  const int kvh = blockIdx.y;
+  const int split = OUTER ? blockIdx.z & (num_splits - 1) : blockIdx.z;
+  const int part = OUTER ? blockIdx.z >> (31 - __clz(num_splits)) : 0;
+  const int parts = OUTER ? outer.parts : 1;
   const int groups = hq / hkv;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int slot = t >= 0 ? slot_of_token[t] : -1;  // (a list of rows may be padded with -1)
@@ -140,8 +157,9 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
   const int first_key = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
   const int tile_lo = first_key / DCL_TILE, tile_hi = pos / DCL_TILE;
   const int ntiles = tile_hi - tile_lo + 1;
-  const int per_split = (ntiles + num_splits - 1) / num_splits;
-  const int my_lo = tile_lo + split * per_split;
+  const int runs = num_splits * parts;  // the pair's tiles in this many runs, one per block
+  const int per_split = (ntiles + runs - 1) / runs;
+  const int my_lo = tile_lo + (part * num_splits + split) * per_split;
   const int my_hi = live ? min(my_lo + per_split - 1, tile_hi) : my_lo - 1;
   const int* table = block_table + (size_t)(live ? slot : 0) * max_pages;
   const size_t page_elems = (size_t)hkv * page_size * HD;
@@ -425,10 +443,51 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
         l += lk[k] * f;
         o += ok[k] * f;
       }
-      if (live) out[((size_t)t * hq + kvh * groups + r) * HD + d] = __float2bfloat16_rn(l > 0.f ? __fdividef(o, l) : 0.f);
+      if (OUTER) {
+        float* mine = outer.scratch + ((size_t)(blockIdx.x * hkv + kvh) * parts + part) * (total + 32);
+        __stcg(mine + e, o);
+        if (d == 0) {
+          __stcg(mine + total + r, m);
+          __stcg(mine + total + 16 + r, l);
+        }
+      } else if (live) {
+        out[((size_t)t * hq + kvh * groups + r) * HD + d] = __float2bfloat16_rn(l > 0.f ? __fdividef(o, l) : 0.f);
+      }
     }
   }
   MS_TIMELINE_MARK(4);
+  if constexpr (!OUTER) return;
+
+  // The cluster's sums are in global memory.  Its first block counts the cluster; the one that counts last merges the
+  // parts in their order.
+  __shared__ int last_s;
+  __threadfence();
+  cluster.sync();
+  if (split != 0) return;
+  int* counter = outer.counters + blockIdx.x * hkv + kvh;
+  if (tid == 0) {
+    __threadfence();
+    last_s = atomicAdd(counter, 1) == parts - 1;
+  }
+  __syncthreads();
+  if (!last_s) return;
+  __threadfence();
+  const float* all = outer.scratch + (size_t)(blockIdx.x * hkv + kvh) * parts * (total + 32);
+  for (int e = tid; e < total; e += DCL_THREADS) {
+    const int r = e / HD;
+    float m = -INFINITY;
+    for (int k = 0; k < parts; ++k) m = fmaxf(m, __ldcg(all + (size_t)k * (total + 32) + total + r));
+    float l = 0.f, o = 0.f;
+    for (int k = 0; k < parts; ++k) {
+      const float* pk = all + (size_t)k * (total + 32);
+      const float mk = __ldcg(pk + total + r);
+      const float f = mk == -INFINITY ? 0.f : ms_exp2(mk - m);
+      l += __ldcg(pk + total + 16 + r) * f;
+      o += __ldcg(pk + e) * f;
+    }
+    if (live) out[((size_t)t * hq + kvh * groups + r) * HD + (e - r * HD)] = __float2bfloat16_rn(l > 0.f ? __fdividef(o, l) : 0.f);
+  }
+  if (tid == 0) *counter = 0;
 }
 
 static size_t dcl_smem_bytes(int hd, int stages, int DCL_WARPS) {
@@ -438,13 +497,13 @@ static size_t dcl_smem_bytes(int hd, int stages, int DCL_WARPS) {
   return tiles > red ? tiles : red;
 }
 
-template <int HD, bool FUSED, int KPW, int DCL_WARPS>
+template <int HD, bool FUSED, int KPW, int DCL_WARPS, bool OUTER>
 static int launch_decode_cluster_k(const void* q, DclRaw raw, const void* k_pages, const void* v_pages, void* out, const int* rows,
                                  const int* positions, const int* slot_of_token, const int* block_table,
                                  int max_pages, int num_pages, int tokens, int hq, int hkv, int page_size, int window,
-                                 float scale, int num_splits, int stages, cudaStream_t stream) {
+                                 float scale, int num_splits, int stages, DclOuter outer, cudaStream_t stream) {
   const size_t smem = dcl_smem_bytes(HD, stages, DCL_WARPS);
-  auto kern = attention_decode_cluster_kernel<HD, FUSED, KPW, DCL_WARPS>;
+  auto kern = attention_decode_cluster_kernel<HD, FUSED, KPW, DCL_WARPS, OUTER>;
   static size_t configured = 0;  // per instantiation: the largest size asked for so far
   if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -457,7 +516,7 @@ static int launch_decode_cluster_k(const void* q, DclRaw raw, const void* k_page
     configured = smem;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(tokens, hkv, num_splits);
+  cfg.gridDim = dim3(tokens, hkv, num_splits * outer.parts);
   cfg.blockDim = dim3(DCL_WARPS * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
@@ -481,7 +540,7 @@ static int launch_decode_cluster_k(const void* q, DclRaw raw, const void* k_page
                    cudaLaunchKernelEx(&cfg, kern, (const __nv_bfloat16*)q, raw, (__nv_bfloat16*)k_pages,
                                       (__nv_bfloat16*)v_pages, (__nv_bfloat16*)out, rows, positions, slot_of_token,
                                       block_table, max_pages, num_pages, hq, hkv, page_size, window, scale * MS_LOG2E,
-                                      num_splits, stages));
+                                      num_splits, stages, outer));
   return 0;
 }
 
@@ -490,11 +549,22 @@ template <int HD, bool FUSED>
 static int launch_decode_cluster(const void* q, DclRaw raw, const void* k_pages, const void* v_pages, void* out, const int* rows,
                                  const int* positions, const int* slot_of_token, const int* block_table,
                                  int max_pages, int num_pages, int tokens, int hq, int hkv, int page_size, int window,
-                                 float scale, int num_splits, int stages, int warps, int kpw, cudaStream_t stream) {
-#define MS_DCL_LAUNCH(KPW, WARPS)                                                                                        \
-  return launch_decode_cluster_k<HD, FUSED, KPW, WARPS>(q, raw, k_pages, v_pages, out, rows, positions, slot_of_token,   \
-                                                        block_table, max_pages, num_pages, tokens, hq, hkv, page_size,   \
-                                                        window, scale, num_splits, stages, stream)
+                                 float scale, int num_splits, int stages, int warps, int kpw, DclOuter outer, cudaStream_t stream) {
+  // (several clusters a pair: built for the two common head sizes only)
+#define MS_DCL_LAUNCH(KPW, WARPS)                                                                                              \
+  do {                                                                                                                         \
+    if constexpr (HD == 64 || HD == 128) {                                                                                     \
+      if (outer.parts > 1)                                                                                                     \
+        return launch_decode_cluster_k<HD, FUSED, KPW, WARPS, true>(q, raw, k_pages, v_pages, out, rows, positions,           \
+                                                                    slot_of_token, block_table, max_pages, num_pages, tokens, \
+                                                                    hq, hkv, page_size, window, scale, num_splits, stages,    \
+                                                                    outer, stream);                                           \
+    }                                                                                                                          \
+    return launch_decode_cluster_k<HD, FUSED, KPW, WARPS, false>(q, raw, k_pages, v_pages, out, rows, positions,              \
+                                                                 slot_of_token, block_table, max_pages, num_pages, tokens,    \
+                                                                 hq, hkv, page_size, window, scale, num_splits, stages,       \
+                                                                 outer, stream);                                              \
+  } while (0)
   // few tiles a round, or wide heads (a long chain of steps per key): smaller parts keep every warp busy
   if (kpw == 0) kpw = warps == 8 ? 32 : HD > 64 ? 16 : stages <= 4 ? 32 : 64;
   if (warps == 8 && kpw == 64) kpw = 32;
@@ -518,8 +588,19 @@ static int decode_cluster_dispatch(const void* q, const DclRaw* raw, void* k_pag
                                    const int* rows, const int* positions, const int* slot_of_token,
                                    const int* block_table, int max_pages, int num_pages, int tokens, int hq, int hkv,
                                    int hd, int page_size, int window, float scale, int num_splits, int stages,
-                                   int warps, int kpw, cudaStream_t stream) {
+                                   int warps, int kpw, int parts, float* scratch, long long scratch_words, int* counters,
+                                   int num_counters, cudaStream_t stream) {
   if (tokens == 0) return 0;
+  MS_REQUIRE(parts >= 1 && parts <= DCL_MAX_PARTS, "attention_decode_cluster: %d clusters a pair; 1 to %d", parts, DCL_MAX_PARTS);
+  if (parts > 1) {
+    const long long need = (long long)tokens * hkv * parts * ((hq / (hkv > 0 ? hkv : 1)) * hd + 32);
+    MS_REQUIRE(num_splits > 1, "attention_decode_cluster: several clusters a pair need clusters of more than one block");
+    MS_REQUIRE(hd == 64 || hd == 128, "attention_decode_cluster: several clusters a pair are built for head sizes 64 and 128, not %d", hd);
+    MS_REQUIRE(scratch != nullptr && counters != nullptr && scratch_words >= need && num_counters >= tokens * hkv,
+               "attention_decode_cluster: %d clusters a pair need %lld words of scratch and %d counters; %lld and %d were given",
+               parts, need, tokens * hkv, scratch ? scratch_words : 0LL, counters ? num_counters : 0);
+  }
+  const DclOuter outer = {parts, scratch, counters};
   MS_REQUIRE(warps == 4 || warps == 8, "attention_decode_cluster: 4 or 8 warps a block, not %d", warps);
   MS_REQUIRE(kpw == 0 || kpw == 16 || kpw == 32 || kpw == 64, "attention_decode_cluster: a warp takes 16, 32 or 64 keys at a time (0: by rule), not %d", kpw);
   MS_REQUIRE(tokens > 0 && hq > 0 && hkv > 0 && hq % hkv == 0 && hkv <= 65535, "attention_decode_cluster: bad head counts hq=%d hkv=%d", hq, hkv);
@@ -535,7 +616,7 @@ static int decode_cluster_dispatch(const void* q, const DclRaw* raw, void* k_pag
   case N:                                                                                                           \
     return launch_decode_cluster<N, FUSED>(q, FUSED ? *raw : none, k_pages, v_pages, out, rows, positions, slot_of_token, \
                                            block_table, max_pages, num_pages, tokens, hq, hkv, page_size, window, scale, \
-                                           num_splits, stages, warps, kpw, stream)
+                                           num_splits, stages, warps, kpw, outer, stream)
   switch (hd) {
     MS_DCL_CASE(16);
     MS_DCL_CASE(32);

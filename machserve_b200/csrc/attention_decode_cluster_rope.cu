@@ -13,7 +13,8 @@ MS_API int ms_attention_decode_cluster_rope(const void* qkv, int ld, const float
                                             const int* positions, const int* slot_of_token, const int* block_table,
                                             int max_pages, int num_pages, int tokens, int hq, int hkv, int hd,
                                             int page_size, int window, float scale, int num_splits, int stages,
-                                            int warps, int keys_per_warp, cudaStream_t stream) {
+                                            int warps, int keys_per_warp, int parts, float* scratch, long long scratch_words,
+                                       int* counters, int num_counters, cudaStream_t stream) {
   MS_REQUIRE(qkv != nullptr && cos_sin != nullptr, "attention_decode_cluster_rope: no rows or no rotary table");
   MS_REQUIRE(ld % 8 == 0 && ld >= (hq + (store ? 2 * hkv : 0)) * hd, "attention_decode_cluster_rope: row stride %d (a multiple of 8, at least %d)",
              ld, (hq + (store ? 2 * hkv : 0)) * hd);
@@ -22,5 +23,5 @@ MS_API int ms_attention_decode_cluster_rope(const void* qkv, int ld, const float
   const DclRaw raw = {(const __nv_bfloat16*)qkv, ld, bias, (const float2*)cos_sin, store ? 1 : 0};
   return decode_cluster_dispatch<true>(nullptr, &raw, k_pages, v_pages, out, rows, positions, slot_of_token, block_table,
                                  max_pages, num_pages, tokens, hq, hkv, hd, page_size, window, scale, num_splits, stages,
-                                 warps, keys_per_warp, stream);
+                                 warps, keys_per_warp, parts, scratch, scratch_words, counters, num_counters, stream);
 }

@@ -73,8 +73,8 @@ class _Signatures:
     ms_attention_generic = [P, P, P, P, I, I, P, P, P, I, I, I, I, I, I, I, I, F, I, P]
     ms_gemm_f32 = [P, I, P, P, P, I, I, I, I, P]
     ms_attention_decode = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P]
-    ms_attention_decode_cluster = [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, I, I, P]
-    ms_attention_decode_cluster_rope = [P, I, P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, I, I, P]
+    ms_attention_decode_cluster = [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, I, I, I, P, LL, P, I, P]
+    ms_attention_decode_cluster_rope = [P, I, P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, I, I, I, P, LL, P, I, P]
     ms_attention_prefill_tc = [P, P, P, P, I, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, LL, P, LL, P]
     ms_attention_prefill_tc_plan = [I, I, I, I, I, I, I, P]
     ms_attention_prefill = [P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P]
@@ -364,12 +364,35 @@ def attention_decode_cluster_blocks_per_sm(head_dim: int, stages: int, warps: in
     return int(lib().ms_attention_decode_cluster_blocks_per_sm(int(head_dim), int(stages), int(warps)))
 
 
+def attention_decode_cluster_scratch_words(tokens: int, num_heads: int, num_kv_heads: int, head_dim: int, parts: int) -> int:
+    """float32 words of scratch for `parts` > 1 clusters per (row, kv head); beside them, tokens * num_kv_heads int32
+    counters that are zero before the first launch."""
+    fn = lib().ms_attention_decode_cluster_scratch_words
+    fn.restype = c_longlong
+    return int(fn(int(tokens), int(num_heads), int(num_kv_heads), int(head_dim), int(parts)))
+
+
+def _outer_args(name, tokens, num_heads, num_kv_heads, head_dim, parts, scratch, counters):
+    if parts <= 1:
+        return 1, None, 0, None, 0
+    need = attention_decode_cluster_scratch_words(tokens, num_heads, num_kv_heads, head_dim, parts)
+    _need(scratch is not None and scratch.dtype == torch.float32 and scratch.is_contiguous() and scratch.numel() >= need,
+          f"{name}: {parts} clusters a row need {need} float32 words of scratch")
+    _need(counters is not None and counters.dtype == torch.int32 and counters.is_contiguous() and counters.numel() >= tokens * num_kv_heads,
+          f"{name}: {parts} clusters a row need {tokens * num_kv_heads} int32 counters")
+    return int(parts), _ptr(scratch), scratch.numel(), _ptr(counters), counters.numel()
+
+
 def attention_decode_cluster(q, k_pages, v_pages, out, positions, slot_of_token, block_table, num_heads, num_kv_heads,
-                             head_dim, window, scale, num_splits, stages, rows=None, num_rows=None, warps=4, keys_per_warp=0):
+                             head_dim, window, scale, num_splits, stages, rows=None, num_rows=None, warps=4, keys_per_warp=0,
+                             parts=1, scratch=None, counters=None):
     """As attention_decode, with the splits of a row held by one thread-block cluster (1, 2, 4 or 8) and merged in
     shared memory: no scratch.  Keys and values of earlier positions are requested before the kernel waits for its
-    predecessor in the stream.  `stages`: tiles of 64 keys a block holds at once."""
+    predecessor in the stream.  `stages`: tiles of 64 keys a block holds at once.  `parts` > 1 (few rows with long
+    contexts): a row's keys go to that many clusters, which leave their sums in `scratch`; the one that ends last
+    merges them in order (`counters`: int32 zeros, left zero)."""
     tokens = q.shape[0] if rows is None else int(num_rows)
+    outer = _outer_args("attention_decode_cluster", tokens, num_heads, num_kv_heads, head_dim, parts, scratch, counters)
     _need(rows is None or (rows.dtype == torch.int32 and rows.numel() >= tokens), "attention_decode_cluster: bad row list")
     _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16,
           "attention_decode_cluster: bfloat16 only")
@@ -381,7 +404,7 @@ def attention_decode_cluster(q, k_pages, v_pages, out, positions, slot_of_token,
         lib().ms_attention_decode_cluster(
             _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(rows), _ptr(positions), _ptr(slot_of_token),
             _ptr(block_table), block_table.shape[1], k_pages.shape[0], tokens, num_heads, num_kv_heads, head_dim,
-            k_pages.shape[2], int(window or 0), float(scale), int(num_splits), int(stages), int(warps), int(keys_per_warp), _stream(),
+            k_pages.shape[2], int(window or 0), float(scale), int(num_splits), int(stages), int(warps), int(keys_per_warp), *outer, _stream(),
         ),
         "attention_decode_cluster",
     )
@@ -390,11 +413,12 @@ def attention_decode_cluster(q, k_pages, v_pages, out, positions, slot_of_token,
 
 def attention_decode_cluster_rope(qkv, bias, cos_sin, store, k_pages, v_pages, out, positions, slot_of_token, block_table,
                                   num_heads, num_kv_heads, head_dim, window, scale, num_splits, stages, rows=None,
-                                  num_rows=None, warps=4, keys_per_warp=0):
+                                  num_rows=None, warps=4, keys_per_warp=0, parts=1, scratch=None, counters=None):
     """rope_kv_store and attention_decode_cluster in one kernel, for rows that are alone in their sequences: reads
     rows of q|k|v (k and v only if `store`) as the projection left them, adds the bias, rotates q and k (full rotary,
     pairs j and j + head_dim/2, table [positions, head_dim/2, 2]), writes k and v into the cache, and attends."""
     tokens = qkv.shape[0] if rows is None else int(num_rows)
+    outer = _outer_args("attention_decode_cluster_rope", tokens, num_heads, num_kv_heads, head_dim, parts, scratch, counters)
     _need(rows is None or (rows.dtype == torch.int32 and rows.numel() >= tokens), "attention_decode_cluster_rope: bad row list")
     _need(qkv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16 and
           v_pages.dtype == torch.bfloat16, "attention_decode_cluster_rope: bfloat16 only")
@@ -413,7 +437,7 @@ def attention_decode_cluster_rope(qkv, bias, cos_sin, store, k_pages, v_pages, o
             _ptr(qkv), qkv.stride(0), _ptr(bias), _ptr(cos_sin), 1 if store else 0, _ptr(k_pages), _ptr(v_pages), _ptr(out),
             _ptr(rows), _ptr(positions), _ptr(slot_of_token), _ptr(block_table), block_table.shape[1], k_pages.shape[0],
             tokens, num_heads, num_kv_heads, head_dim, k_pages.shape[2], int(window or 0), float(scale), int(num_splits),
-            int(stages), int(warps), int(keys_per_warp), _stream(),
+            int(stages), int(warps), int(keys_per_warp), *outer, _stream(),
         ),
         "attention_decode_cluster_rope",
     )

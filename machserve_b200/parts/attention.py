@@ -227,7 +227,7 @@ class Attention(Mixer):
         return self.attend(ctx, self.encode_store(ctx, qkv, cache, store), cache, out)
 
     def _single_launch(self, units: int, tiles: int):
-        """(splits, stages, warps, keys per warp) for `units` (row, kv head) pairs whose longest run of keys has `tiles`
+        """(splits, stages, warps, keys per warp, clusters per pair) for `units` (row, kv head) pairs whose longest run of keys has `tiles`
         tiles of 64.  What the measurements on B200 (head sizes 64 and 128, 8 to 64 rows, 1,000 to 2,048 keys) come to:
         all blocks of the launch are resident at once (a second wave costs more than fewer, longer blocks), as many
         splits as that allows up to three and a half blocks per SM, never more blocks than half the tiles.  A block
@@ -252,6 +252,22 @@ class Attention(Mixer):
             if choice:
                 break
         splits, stages, per = choice or (1, min(2, self.max_stages, tiles), tiles)
+        # Few rows with long contexts leave most SMs without a block: a pair's keys then go to `parts` clusters, whose
+        # sums meet in scratch memory (about 4 us more).  Measured (1 to 8 rows, 8,192 and 32,768 keys, both head sizes):
+        # worth it while the launch stays at one block per SM and a block keeps four tiles, or, for long runs, at two
+        # blocks per SM and sixteen tiles.
+        parts = 1
+        while splits == 8 and parts < 16 and hd in (64, 128):  # (the head sizes the kernel has this form for)
+            blocks, run = 8 * units * 2 * parts, tiles // (8 * 2 * parts)
+            if not ((blocks <= 2 * sm and run >= 16) or (8 * units <= sm // 4 and blocks <= sm and run >= 4)):
+                break
+            parts *= 2
+        if parts > 1:
+            per = -(-tiles // (8 * parts))
+            stages = min(per, self.max_stages)
+            warps = 8 if hd <= 64 and 8 * units * parts <= sm else 4
+            self._launch_cache[key] = (splits, stages, warps, 0, parts)
+            return self._launch_cache[key]
         blocks = splits * units
         # the few blocks of a small batch (one per SM at most): eight warps, with half a tile each when the block holds its
         # whole run, with a quarter each when it goes through a ring (of two places of two tiles); else four warps, and
@@ -259,7 +275,7 @@ class Attention(Mixer):
         ring = 2 <= stages < per
         warps = 8 if stages >= 4 and blocks <= sm and hd <= 64 else 4
         kpw = 16 if ring else 0
-        self._launch_cache[key] = (splits, stages, warps, kpw)
+        self._launch_cache[key] = (splits, stages, warps, kpw, 1)
         return self._launch_cache[key]
 
     def _attend_single(self, ctx, q, cache, out, raw=None):
@@ -270,18 +286,25 @@ class Attention(Mixer):
         tiles = (work.shape[0] * self.CONTEXT_BUCKET + 63) // 64  # of the longest decoding context, by bucket
         if self.window:
             tiles = min(tiles, (self.window + 63) // 64 + 1)
-        splits, stages, warps, kpw = self._single_launch(t * self.hkv, tiles)
+        splits, stages, warps, kpw, parts = self._single_launch(t * self.hkv, tiles)
+        scratch = counters = None
+        if parts > 1:
+            words = ops.attention_decode_cluster_scratch_words(t, self.hq, self.hkv, self.hd, parts)
+            scratch = rt.workspace.get("attn.decode_parts", (words,), torch.float32)
+            # (a buffer of its own: zero when made, left zero by every launch)
+            counters = rt.workspace.get("attn.decode_counters", (t * self.hkv,), torch.int32, zero=True)
         if raw is not None:
             qkv, store = raw
             return ops.attention_decode_cluster_rope(
                 qkv, self.bias, self.table, store, cache.k_pages, cache.v_pages, out, ctx.positions, ctx.slot_of_token,
                 table, self.hq, self.hkv, self.hd, self.window, self.scale, splits, stages, warps=warps, keys_per_warp=kpw,
+                parts=parts, scratch=scratch, counters=counters,
             )
         return ops.attention_decode_cluster(
             q, cache.k_pages, cache.v_pages, out, ctx.positions, ctx.slot_of_token, table, self.hq, self.hkv,
             self.hd, self.window, self.scale, splits, stages,
             rows=None if work.sizes["tile_row0"] == 0 and t == q.shape[0] else work.lists["single_rows"], num_rows=t, warps=warps,
-            keys_per_warp=kpw,
+            keys_per_warp=kpw, parts=parts, scratch=scratch, counters=counters,
         )
 
     def attend(self, ctx, q, cache, out):

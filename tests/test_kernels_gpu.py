@@ -368,6 +368,79 @@ def test_attention_decode_cluster(lens, hq, hkv, hd, page, window, splits, stage
 
 
 @pytest.mark.parametrize("lens,hq,hkv,hd,page,window", ATT_CASES)
+@pytest.mark.parametrize("splits,stages,warps,kpw,parts", [(8, 2, 4, 0, 2), (8, 5, 8, 0, 4), (4, 1, 4, 16, 3), (2, 8, 4, 0, 16), (8, 4, 4, 16, 8)])
+def test_attention_decode_cluster_in_several_clusters(lens, hq, hkv, hd, page, window, splits, stages, warps, kpw, parts):
+    """A row's keys spread over several clusters (few rows with long contexts): each leaves its sums in scratch memory,
+    the one that ends last merges them in order.  Against the plain reference, with a far key that stands out, rows
+    whose few keys leave most clusters without any, a padding row, a list of rows; launched twice on the same scratch
+    and counters (which every launch leaves zero); and the fused form against the two kernels it stands for."""
+    import torch
+    from machserve_b200 import ops
+    from machserve_b200.config import part
+    from machserve_b200.parts import Runtime, Workspace
+    from machserve_b200.parts.rope import RotaryEncoding
+    if not ops.attention_decode_supports(hd, hq // hkv):
+        pytest.skip("size not covered by the fast kernel (the engine then uses the exact kernel)")
+    stages = min(stages, ops.attention_decode_cluster_max_stages(hd))
+    case = PagedCase(lens, hq, hkv, hd, page, window, seed=20 + parts)
+    rows = [(s, p) for s, n in enumerate(lens) for p in sorted({0, n // 2, n - 1, max(0, n - 2), min(n - 1, 63), min(n - 1, 64)})]
+    far = (len(rows) - 1, hq - 1, max(0, rows[-1][1] - window + 1) if window else 1)
+    q, want, pos, slot = case.queries(rows, scale_one=far)
+    n = len(rows) + 1
+    q16 = torch.cat([T(q, torch.bfloat16), torch.zeros((1, hq * hd), dtype=torch.bfloat16, device=dev())])
+    pos1 = torch.cat([pos, torch.zeros(1, dtype=torch.int32, device=dev())])
+    slot1 = torch.cat([slot, torch.full((1,), -1, dtype=torch.int32, device=dev())])  # a padding row at the end
+    words = ops.attention_decode_cluster_scratch_words(n, hq, hkv, hd, parts)
+    scratch = torch.full((words,), float("nan"), dtype=torch.float32, device=dev())
+    counters = torch.zeros(n * hkv, dtype=torch.int32, device=dev())
+    kw = dict(warps=warps, keys_per_warp=kpw, parts=parts, scratch=scratch, counters=counters)
+    if hd not in (64, 128):  # built for the two common head sizes; the others are refused, by name
+        with pytest.raises(ops.KernelError, match="head sizes 64 and 128"):
+            ops.attention_decode_cluster(q16, case.k_pages, case.v_pages, torch.empty_like(q16), pos1, slot1, case.table, hq, hkv, hd,
+                                         window, hd ** -0.5, splits, stages, **kw)
+        return
+    for _ in range(2):
+        out = torch.full((n, hq * hd), 7.0, dtype=torch.bfloat16, device=dev())
+        ops.attention_decode_cluster(q16, case.k_pages, case.v_pages, out, pos1, slot1, case.table, hq, hkv, hd, window,
+                                     hd ** -0.5, splits, stages, **kw)
+        assert np.abs(N(out[:-1]) - want).max() <= 2.0 ** -7 * max(1.0, np.abs(want).max())
+        assert (N(out[-1]) == 7.0).all()  # nothing is written for the padding row
+        assert not counters.any()
+    pick = np.array(sorted(set(range(0, len(rows), 2)) | {len(rows) - 1}), dtype=np.int32)
+    out2 = torch.full((n, hq * hd), 7.0, dtype=torch.bfloat16, device=dev())
+    ops.attention_decode_cluster(q16, case.k_pages, case.v_pages, out2, pos1, slot1, case.table, hq, hkv, hd, window,
+                                 hd ** -0.5, splits, stages, rows=T(pick), num_rows=len(pick), **kw)
+    assert torch.equal(out2[T(pick).long()], out[T(pick).long()])
+    assert (N(out2)[np.setdiff1d(np.arange(len(rows)), pick)] == 7.0).all()
+    with pytest.raises(ops.KernelError, match="scratch"):
+        ops.attention_decode_cluster(q16, case.k_pages, case.v_pages, out2, pos1, slot1, case.table, hq, hkv, hd, window,
+                                     hd ** -0.5, splits, stages, warps=warps, keys_per_warp=kpw, parts=parts, scratch=scratch[:-1],
+                                     counters=counters)
+    # the fused form: one row per sequence at its end, its key and value written by the block whose run holds the position
+    rng = np.random.default_rng(5)
+    last = [(s, n_ - 1) for s, n_ in enumerate(lens)]
+    pos_l = np.array([p for _, p in last], dtype=np.int32)
+    slot_l = np.array([case.slots[s] for s, _ in last], dtype=np.int32)
+    pe = RotaryEncoding(part("rope", head_dim=hd, rotary_dim=hd, theta=30000.0, pairing="half"))
+    table = pe.rotary_table(Runtime(torch.bfloat16, dev(), Workspace(dev()), max(lens) + 1))
+    width = (hq + 2 * hkv) * hd
+    qkv = T(rng.normal(size=(len(last), width)), torch.bfloat16)
+    bias = T(rng.normal(size=width).astype(np.float32))
+    k1, v1 = case.k_pages.clone(), case.v_pages.clone()
+    q1 = torch.zeros((len(last), hq * hd), dtype=torch.bfloat16, device=dev())
+    ops.rope_kv_store(qkv, bias, T(pos_l), T(slot_l), case.table, table, hd, False, q1, k1, v1, hq, hkv, hd)
+    two = torch.empty((len(last), hq * hd), dtype=torch.bfloat16, device=dev())
+    ops.attention_decode_cluster(q1, k1, v1, two, T(pos_l), T(slot_l), case.table, hq, hkv, hd, window, hd ** -0.5, splits, stages, **kw)
+    k2, v2 = case.k_pages.clone(), case.v_pages.clone()
+    one = torch.empty_like(two)
+    ops.attention_decode_cluster_rope(qkv, bias, table, True, k2, v2, one, T(pos_l), T(slot_l), case.table, hq, hkv, hd,
+                                      window, hd ** -0.5, splits, stages, **kw)
+    assert torch.equal(k1, k2) and torch.equal(v1, v2)
+    assert np.abs(N(one) - N(two)).max() <= 2.0 ** -8 * max(1.0, np.abs(N(two)).max())
+    assert not counters.any()
+
+
+@pytest.mark.parametrize("lens,hq,hkv,hd,page,window", ATT_CASES)
 @pytest.mark.parametrize("splits,stages,store,warps", [(1, 1, True, 4), (2, 8, True, 4), (4, 2, True, 4), (8, 1, True, 4), (8, 8, False, 4),
                                                        (2, 1, False, 4), (1, 4, True, 8), (8, 8, True, 8), (2, 5, False, 8)])
 def test_attention_decode_cluster_rope(lens, hq, hkv, hd, page, window, splits, stages, store, warps):

@@ -146,3 +146,31 @@ def test_first_tokens(model_root, name, dtype):
     got = collect_rows(steps, _replay(d, dtype, steps, 192, TINY[name]["page"]))
     for rid, want in _reference(d, dtype, {"a": a, "b": b, "c": c}).items():
         assert_close(got[rid], want, _tol(dtype), f"tiny-{name} {dtype} first tokens {rid}")
+
+
+def test_decoding_one_request_with_a_long_context(model_root):
+    """One request with 4,400 tokens of context, decoded token by token in bfloat16 at head size 64: with so few rows and
+    so many keys the attention spreads a row's keys over several clusters, whose sums meet in scratch memory (the test
+    checks that this form was chosen).  The logits of the 8 decoded positions are compared with the plain implementation."""
+    import torch
+    from machserve_b200 import ModelRunner
+    from machserve_b200.engine.runner import StepEntry
+    from machserve_b200.parts.attention import Attention
+
+    d = make_model_dir(model_root, "D", max_position_embeddings=8192)
+    vocab, page = TINY["D"]["config"]["vocab_size"], TINY["D"]["page"]
+    toks = random_tokens(vocab, 4408, 77)
+    runner = ModelRunner.from_model_dir(d, dtype="bfloat16", page_size=page, num_pages=4608 // page, max_requests=2,
+                                        max_step_tokens=1024, max_seq_len=4608)
+    at = 0
+    while at < 4400:
+        n = min(1024, 4400 - at)
+        runner.step([StepEntry("a", toks[at : at + n], [])])
+        at += n
+    rows = []
+    for i in range(8):
+        rows.append(runner.step([StepEntry("a", [toks[4400 + i]], [0])]).detach().float().cpu().numpy()[0].copy())
+    attention = next(p for p in runner.model.parts() if isinstance(p, Attention))
+    assert any(choice[4] > 1 for choice in attention._launch_cache.values()), attention._launch_cache
+    want = plain_logits(d, toks, bf16_weights=True)[4400:4408]
+    assert_close(np.stack(rows), want, BF16_TOL, "tiny-D bfloat16, decoding after 4,400 tokens")
