@@ -255,11 +255,12 @@ class Attention(Mixer):
         # Few rows with long contexts leave most SMs without a block: a pair's keys then go to `parts` clusters, whose
         # sums meet in scratch memory (about 4 us more).  Measured (1 to 8 rows, 8,192 and 32,768 keys, both head sizes):
         # worth it while the launch stays at one block per SM and a block keeps four tiles, or, for long runs, at two
-        # blocks per SM and sixteen tiles.
+        # blocks per SM and 32 tiles (inside a step, a second block per SM delays the kernels that follow, which
+        # start early to request their weights: batch 8 at 16,384 keys lost 4 % with runs of 16 tiles).
         parts = 1
         while splits == 8 and parts < 16 and hd in (64, 128):  # (the head sizes the kernel has this form for)
             blocks, run = 8 * units * 2 * parts, tiles // (8 * 2 * parts)
-            if not ((blocks <= 2 * sm and run >= 16) or (8 * units <= sm // 4 and blocks <= sm and run >= 4)):
+            if not ((blocks <= 2 * sm and run >= 32) or (8 * units <= sm // 4 and blocks <= sm and run >= 4)):
                 break
             parts *= 2
         if parts > 1:
