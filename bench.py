@@ -653,7 +653,7 @@ def main() -> int:
     a.warmup = max(a.warmup, 3)
     only = {x.strip() for x in a.only.split(",") if x.strip()}
     if a.profile:
-        only = {"headline"}
+        only = {"mixed_7b"} if a.profile == "mixed" else {"headline"}
 
     import torch
 
