@@ -364,6 +364,228 @@ attention_generic_rows_kernel(const TA* __restrict__ q, const TC* __restrict__ k
   }
 }
 
+// The heads form once more, for float32 rows that are alone in their sequences (decoding), spread over the GPU: the
+// W warps of a (token, group of heads) are W blocks of one warp each in a thread-block cluster, so that a batch of 8
+// rows with 2 key heads is 128 blocks instead of 16.  Warp w is the block of rank w: it takes the tiles w, w + W, ...
+// exactly as above, with the next tile's keys and values on their way (cp.async, two places) while it works on the
+// present one; the partial results go to the shared memory of the block that merges the row (row r: rank r mod W),
+// which merges them in warp order with the arithmetic of the kernels above.  Same bits.
+// Keys are staged with a row stride of hd + 4 floats: 16-byte copies need it, and 16-byte reads of a row per lane do
+// not collide there.  head_dim a multiple of 4, at most 128.
+#include <cooperative_groups.h>
+namespace cg = cooperative_groups;
+
+__device__ __forceinline__ void attg_cp16(float* smem, const float* gmem, bool valid) {
+  const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;  // nothing is read for a key that is not there: the place is filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem), "r"(bytes) : "memory");
+}
+
+template <int W, int NACC, int R>
+__global__ void __launch_bounds__(32)
+attention_generic_cluster_kernel(const float* __restrict__ q, const float* __restrict__ k_pages, const float* __restrict__ v_pages,
+                                 float* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                 const int* __restrict__ block_table, int max_pages, int num_pages, int hq, int hkv, int hd,
+                                 int page_size, int window, float scale) {
+  constexpr int MINE = R > W ? R / W : 1;  // rows this block merges (R: up to this many heads of a group a block; a power of two)
+  extern __shared__ __align__(16) float cl_smem[];
+  const int ks = hd + 4;
+  float* q_s = cl_smem;                               // [R][hd]
+  float* k_buf = q_s + R * hd;                 // [2][32][hd + 4]
+  float* v_buf = k_buf + 2 * 32 * ks;                 // [2][32][hd]
+  float* part = v_buf + 2 * 32 * hd;                  // [MINE][W][hd + 2]: what the W warps found for the rows merged here
+  cg::cluster_group cluster = cg::this_cluster();
+  // (every block says that it runs; the others wait for that, much later, before they write into its shared memory)
+  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+  const int warp = (int)cluster.block_rank(), lane = threadIdx.x;
+  const int groups = hq / hkv;
+  const int per_kv = (groups + R - 1) / R;
+  const int unit = blockIdx.x / W;
+  const int t = unit / (hkv * per_kv), rem = unit - t * (hkv * per_kv);
+  const int kvh = rem / per_kv, g0 = (rem - kvh * per_kv) * R;
+  const int head0 = kvh * groups + g0, live_rows = min(R, groups - g0);
+  const int seq = seq_of_token[t];
+  const int pos = seq >= 0 ? positions[t] : -1;  // (a padding row has no tiles, and takes part in the barrier)
+  const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const size_t head_off = (size_t)kvh * page_size * hd;
+  const size_t page_elems = (size_t)hkv * page_size * hd;
+  const int* table = block_table + (size_t)(seq >= 0 ? seq : 0) * max_pages;
+  const int chunks = hd / 4;  // 16-byte pieces of a row
+
+  // requests tile `tile` into place `b`; returns the element offset of this lane's key row (-1: no such key)
+  auto request = [&](int tile, int b) -> long long {
+    const int key = tile * 32 + lane;
+    long long base = -1;
+    if (key >= first && key <= pos) {
+      const int page = table[key / page_size];
+      if (page >= 0 && page < num_pages) base = (long long)((size_t)page * page_elems + head_off + (size_t)(key % page_size) * hd);
+    }
+    float* kb = k_buf + (size_t)b * 32 * ks;
+    float* vb = v_buf + (size_t)b * 32 * hd;
+    for (int c = lane; c < 32 * chunks; c += 32) {
+      const int j = c / chunks, piece = c - j * chunks;
+      const long long bj = __shfl_sync(0xffffffffu, base, j);
+      const bool ok = bj >= 0;
+      attg_cp16(kb + j * ks + piece * 4, ok ? k_pages + bj + piece * 4 : k_pages, ok);
+      attg_cp16(vb + j * hd + piece * 4, ok ? v_pages + bj + piece * 4 : v_pages, ok);
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+    return base;
+  };
+
+  int tile = first / 32 + warp;
+  long long base = -1, base_next = -1;
+  if (tile * 32 <= pos) base = request(tile, 0);
+  for (int e = lane; e < R * hd; e += 32) {
+    const int r = e / hd, d = e - r * hd;
+    q_s[e] = r < live_rows ? q[((size_t)t * hq + head0 + r) * hd + d] : 0.f;
+  }
+  __syncwarp();
+
+  float m[R], l[R], acc[R][NACC];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    m[r] = -INFINITY;
+    l[r] = 0.f;
+#pragma unroll
+    for (int i = 0; i < NACC; ++i) acc[r][i] = 0.f;
+  }
+
+#pragma unroll 1
+  for (int b = 0; tile * 32 <= pos; tile += W, b ^= 1) {
+    const bool more = (tile + W) * 32 <= pos;
+    if (more) {
+      base_next = request(tile + W, b ^ 1);
+      asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    }
+    __syncwarp();
+    const int key = tile * 32 + lane;
+    const float* kr = k_buf + (size_t)b * 32 * ks + lane * ks;
+    const float* my_v = v_buf + (size_t)b * 32 * hd;
+    float dot[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) dot[r] = 0.f;
+    for (int d = 0; d < hd; d += 4) {
+      const float4 kv = *reinterpret_cast<const float4*>(kr + d);
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const float4 qv = *reinterpret_cast<const float4*>(q_s + r * hd + d);
+        dot[r] = fmaf(qv.x, kv.x, dot[r]);
+        dot[r] = fmaf(qv.y, kv.y, dot[r]);
+        dot[r] = fmaf(qv.z, kv.z, dot[r]);
+        dot[r] = fmaf(qv.w, kv.w, dot[r]);
+      }
+    }
+    const bool valid = base >= 0;  // (inside the row's range of keys and with a page)
+    const unsigned vmask = __ballot_sync(0xffffffffu, valid);
+    float pr[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      pr[r] = 0.f;
+      if (r >= live_rows) continue;
+      const float sc = valid ? dot[r] * scale : -INFINITY;
+      const float tile_max = ms_warp_max(sc);
+      const float m_new = fmaxf(m[r], tile_max);
+      pr[r] = (valid && m_new > -INFINITY) ? expf(sc - m_new) : 0.f;
+      const float corr = (m[r] == -INFINITY) ? 0.f : expf(m[r] - m_new);
+      l[r] = l[r] * corr + ms_warp_sum(pr[r]);
+#pragma unroll
+      for (int i = 0; i < NACC; ++i) acc[r][i] *= corr;
+      m[r] = m_new;
+    }
+    for (int j = 0; j < 32; ++j) {
+      if (!((vmask >> j) & 1u)) continue;
+      float vj[NACC];
+#pragma unroll
+      for (int i = 0; i < NACC; ++i) {
+        const int d = lane + 32 * i;
+        vj[i] = d < hd ? my_v[j * hd + d] : 0.f;
+      }
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const float pj = __shfl_sync(0xffffffffu, pr[r], j);
+#pragma unroll
+        for (int i = 0; i < NACC; ++i) acc[r][i] = fmaf(pj, vj[i], acc[r][i]);
+      }
+    }
+    __syncwarp();  // the place is free for the tile after the next
+    base = base_next;
+  }
+
+  // this warp's results go to the blocks that merge the rows
+  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+  const int pw = hd + 2;
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    float* p = cluster.map_shared_rank(part, r % W) + ((size_t)(r / W) * W + warp) * pw;
+#pragma unroll
+    for (int i = 0; i < NACC; ++i) {
+      const int d = lane + 32 * i;
+      if (d < hd) p[d] = acc[r][i];
+    }
+    if (lane == 0) {
+      p[hd] = m[r];
+      p[hd + 1] = l[r];
+    }
+  }
+  cluster.sync();
+#pragma unroll 1
+  for (int k = 0; k < MINE; ++k) {
+    const int r = k * W + warp;
+    if (r >= live_rows || seq < 0) continue;
+    const float* mine = part + (size_t)k * W * pw;
+    float mm = -INFINITY;
+    for (int w = 0; w < W; ++w) mm = fmaxf(mm, mine[(size_t)w * pw + hd]);
+    float f[W], ll = 0.f;
+    for (int w = 0; w < W; ++w) {
+      const float* p = mine + (size_t)w * pw;
+      f[w] = p[hd + 1] > 0.f ? expf(p[hd] - mm) : 0.f;
+      ll += p[hd + 1] * f[w];
+    }
+    const float inv = ll > 0.f ? 1.f / ll : 0.f;
+    for (int d = lane; d < hd; d += 32) {
+      float o = 0.f;
+      for (int w = 0; w < W; ++w) o += mine[(size_t)w * pw + d] * f[w];
+      out[((size_t)t * hq + head0 + r) * hd + d] = o * inv;
+    }
+  }
+}
+
+template <int W, int NACC, int R>
+static int launch_attention_generic_cluster(const float* q, const float* k_pages, const float* v_pages, float* out,
+                                            const int* positions, const int* seq_of_token, const int* block_table,
+                                            int max_pages, int num_pages, int tokens, int hq, int hkv, int hd, int page_size,
+                                            int window, float scale, cudaStream_t stream) {
+  const int groups = hq / hkv;
+  const unsigned units = (unsigned)tokens * (unsigned)hkv * (unsigned)((groups + R - 1) / R);
+  const size_t smem = ((size_t)R * hd + 2 * 32 * (size_t)(hd + 4) + 2 * 32 * (size_t)hd + (size_t)(R > W ? R / W : 1) * W * (hd + 2)) * sizeof(float);
+  auto kern = attention_generic_cluster_kernel<W, NACC, R>;
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    MS_REQUIRE(e == cudaSuccess, "attention: cannot get shared memory for the key tiles: %s", cudaGetErrorString(e));
+    configured = smem;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(units * W);
+  cfg.blockDim = dim3(32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = W;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, q, k_pages, v_pages, out, positions, seq_of_token, block_table, max_pages,
+                                           num_pages, hq, hkv, hd, page_size, window, scale);
+  MS_REQUIRE(e == cudaSuccess, "attention_generic: launch failed: %s", cudaGetErrorString(e));
+  return 0;
+}
+
 // q, out: [tokens, hq*hd].  window <= 0: every earlier key is visible.  share_rows: the step has rows that follow one
 // another in a sequence (portions of prompts): eight rows a block share the tiles they read (head sizes up to 128);
 // else the query heads of a token that share a key head do.  The results are the same bits either way.
@@ -376,6 +598,34 @@ MS_API int ms_attention_generic(const void* q, const void* k_pages, const void* 
   MS_REQUIRE(hd > 0 && hd <= ATT_MAX_HD, "attention: head_dim %d is outside (0, %d]", hd, ATT_MAX_HD);
   MS_REQUIRE(page_size > 0 && max_pages > 0 && num_pages > 0, "attention: bad cache sizes");
   const int groups = hq / hkv;
+  if (share_rows <= 0 && act_dtype == MS_F32 && cache_dtype == MS_F32 && hd % 4 == 0 && hd <= 128 &&
+      ((uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)q) % 16 == 0 && (size_t)tokens * hq * 8 < 0x7fffffffu) {
+    // decoding in float32: the warps of a row as blocks of a cluster (same bits as below).  Up to R heads of a group
+    // share a block's tiles: the fewest that keep the launch at about four blocks of one warp per SM at head sizes up to
+    // 64, under three above (measured at 1, 8 and 64 rows of 2,048 keys, 7 and 6 heads a group; share_rows < 0 asks
+    // for R = -share_rows, for such measurements)
+    const long long most = hd <= 64 ? 592 : 400;
+    int r = 1;
+    while (r < 8 && (long long)tokens * hkv * ((groups + r - 1) / r) * (hd <= 64 ? 8 : 4) > most) r <<= 1;
+    if (share_rows < 0) r = -share_rows;
+    MS_REQUIRE(r == 1 || r == 2 || r == 4 || r == 8, "attention: %d heads a block; 1, 2, 4 or 8", r);
+#define MS_ATT_CLUSTER(W, NACC, R)                                                                                        \
+  return launch_attention_generic_cluster<W, NACC, R>((const float*)q, (const float*)k_pages, (const float*)v_pages, (float*)out, \
+                                                      positions, seq_of_token, block_table, max_pages, num_pages, tokens, hq, hkv, \
+                                                      hd, page_size, window, scale, stream)
+    if (hd <= 64) {
+      if (r == 8) MS_ATT_CLUSTER(ATT_MAX_WARPS, 2, 8);
+      if (r == 4) MS_ATT_CLUSTER(ATT_MAX_WARPS, 2, 4);
+      if (r == 2) MS_ATT_CLUSTER(ATT_MAX_WARPS, 2, 2);
+      MS_ATT_CLUSTER(ATT_MAX_WARPS, 2, 1);
+    }
+    if (r == 8) MS_ATT_CLUSTER(4, 4, 8);
+    if (r == 4) MS_ATT_CLUSTER(4, 4, 4);
+    if (r == 2) MS_ATT_CLUSTER(4, 4, 2);
+    MS_ATT_CLUSTER(4, 4, 1);
+#undef MS_ATT_CLUSTER
+  }
+  share_rows = share_rows > 0;
   const bool rows = share_rows && hd <= 128 && tokens > 1;      // rows of portions share their tiles
   const bool heads = !rows && hd <= 128 && groups > 1;          // the heads of a group share theirs
   const unsigned blocks = rows    ? (unsigned)((tokens + ATT_ROWS - 1) / ATT_ROWS) * (unsigned)hq

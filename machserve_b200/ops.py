@@ -300,7 +300,8 @@ def attention_generic(
 ) -> torch.Tensor:
     """The exact paged attention kernel.  q, out [T, Hq*hd]; pages [num_pages, Hkv, page, hd].  `share_rows`: rows that
     follow one another in a sequence (portions of prompts) share the tiles of keys they read, eight rows a block; the
-    results are the same bits either way."""
+    results are the same bits either way.  (A negative `share_rows`, for measurements: the float32 decoding form with
+    that many heads of a group to a block.)"""
     tokens = q.shape[0]
     _need(q.is_contiguous() and out.is_contiguous() and q.dtype == out.dtype, "attention: bad layout")
     _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == v_pages.dtype, "attention: bad pages")
@@ -310,7 +311,7 @@ def attention_generic(
         lib().ms_attention_generic(
             _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _code(q), _code(k_pages), _ptr(positions),
             _ptr(seq_of_token), _ptr(block_table), block_table.shape[1], k_pages.shape[0], tokens, num_heads,
-            num_kv_heads, head_dim, k_pages.shape[2], int(window or 0), float(scale), 1 if share_rows else 0, _stream(),
+            num_kv_heads, head_dim, k_pages.shape[2], int(window or 0), float(scale), int(share_rows), _stream(),
         ),
         "attention_generic",
     )

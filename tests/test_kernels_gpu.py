@@ -300,6 +300,13 @@ def test_attention_generic_rows_that_share_tiles(lens, hq, hkv, hd, page, window
     tol = 2e-6 if dtype == "float32" else 2.0 ** -8
     assert np.abs(N(shared) - want).max() <= tol * max(1.0, np.abs(want).max()) + 1e-6
     assert torch.equal(shared.view(torch.int32 if dtype == "float32" else torch.int16), alone.view(torch.int32 if dtype == "float32" else torch.int16))
+    if dtype == "float32" and hd % 4 == 0 and hd <= 128:
+        # the float32 decoding form (the warps of a row as the blocks of a cluster), with 1 to 8 heads of a group to a block
+        for heads in (1, 2, 4, 8):
+            spread = torch.full((len(rows), hq * hd), 7.0, dtype=case.tdtype, device=dev())
+            ops.attention_generic(T(q, case.tdtype), case.k_pages, case.v_pages, spread, pos, slot, case.table, hq, hkv, hd, window,
+                                  hd ** -0.5, share_rows=-heads)
+            assert torch.equal(spread.view(torch.int32), shared.view(torch.int32)), f"{heads} heads a block"
 
 
 @pytest.mark.parametrize("lens,hq,hkv,hd,page,window", ATT_CASES)
