@@ -110,33 +110,52 @@ gemm_f32_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ 
   }
 }
 
-// The same sums for up to 16 rows (decoding), laid out for streaming the weights: a block of 128 threads takes 8
-// weight rows, thread (n, m) owns out[m][n] and adds its products for k = 0..K-1 in ascending order, exactly as
-// the kernel above does, so a row's result is the same bit for bit whichever of the two computed it.  With 8
-// weight rows per block a matrix of 896 rows is spread over 112 blocks (the kernel above would use 7).
-#define G32S_ROWS 16
-#define G32S_COLS 8
+// The same sums for up to 16 rows (decoding), laid out for streaming the weights: a block of 128 threads takes COLS
+// weight rows for ROWS rows of x (16 x 8, or 8 x 16 when there are at most 8 rows, so that no thread works on a row that
+// is not there); thread (n, m) owns out[m][n] and adds its products for k = 0..K-1 in ascending order, exactly as the
+// kernel above does, so a row's result is the same bit for bit whichever of the kernels computed it.  With 8 weight
+// rows per block a matrix of 896 rows is spread over 112 blocks (the kernel above would use 7).
+// A thread's sum is one chain of dependent multiply-adds; what can be hidden is everything else: the copies of the next
+// 128 k are on their way while this thread adds up the present ones, and the loop over a full stage is unrolled, so
+// that the reads of shared memory for the next steps are issued while the chain waits for itself.
 #define G32S_KT 128
 
-__global__ void __launch_bounds__(G32S_ROWS * G32S_COLS)
+template <int ROWS, int COLS, bool VEC>
+__global__ void __launch_bounds__(ROWS * COLS)
 gemm_f32_small_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ w, const float* __restrict__ bias,
                       float* __restrict__ out, int ldo, int M, int N, int K) {
-  // two stages: the copies of the next 128 k are on their way while this thread adds up the present ones
-  __shared__ __align__(16) float ws[2][G32S_COLS][G32S_KT + 4];
-  __shared__ __align__(16) float xs[2][G32S_ROWS][G32S_KT + 4];
-  const int tid = threadIdx.x, nl = tid >> 4, m = tid & 15;
-  const int n0 = blockIdx.x * G32S_COLS;
+  constexpr int THREADS = ROWS * COLS;
+  __shared__ __align__(16) float ws[2][COLS][G32S_KT + 4];
+  __shared__ __align__(16) float xs[2][ROWS][G32S_KT + 4];
+  const int tid = threadIdx.x, nl = tid / ROWS, m = tid % ROWS;
+  const int n0 = blockIdx.x * COLS;
   auto request = [&](int stage, int k0) {
-    const int gk = k0 + tid;
+    if (VEC) {  // 16 bytes a copy: K, ldx multiples of 4, both operands 16-byte aligned
 #pragma unroll
-    for (int i = 0; i < G32S_COLS; ++i) {  // 8 x 128 weights: a row of 128 consecutive k per 128 threads
-      const bool ok = n0 + i < N && gk < K;
-      g32_cp_async4(&ws[stage][i][tid], ok ? w + (size_t)(n0 + i) * K + gk : w, ok);
-    }
+      for (int e = tid; e < COLS * (G32S_KT / 4); e += THREADS) {
+        const int i = e / (G32S_KT / 4), kq = (e % (G32S_KT / 4)) * 4;
+        const bool ok = n0 + i < N && k0 + kq < K;
+        g32_cp_async16(&ws[stage][i][kq], ok ? w + (size_t)(n0 + i) * K + k0 + kq : w, ok);
+      }
 #pragma unroll
-    for (int i = 0; i < G32S_ROWS; ++i) {
-      const bool ok = i < M && gk < K;
-      g32_cp_async4(&xs[stage][i][tid], ok ? x + (size_t)i * ldx + gk : x, ok);
+      for (int e = tid; e < ROWS * (G32S_KT / 4); e += THREADS) {
+        const int i = e / (G32S_KT / 4), kq = (e % (G32S_KT / 4)) * 4;
+        const bool ok = i < M && k0 + kq < K;
+        g32_cp_async16(&xs[stage][i][kq], ok ? x + (size_t)i * ldx + k0 + kq : x, ok);
+      }
+    } else {
+#pragma unroll
+      for (int e = tid; e < COLS * G32S_KT; e += THREADS) {
+        const int i = e / G32S_KT, kk = e % G32S_KT;
+        const bool ok = n0 + i < N && k0 + kk < K;
+        g32_cp_async4(&ws[stage][i][kk], ok ? w + (size_t)(n0 + i) * K + k0 + kk : w, ok);
+      }
+#pragma unroll
+      for (int e = tid; e < ROWS * G32S_KT; e += THREADS) {
+        const int i = e / G32S_KT, kk = e % G32S_KT;
+        const bool ok = i < M && k0 + kk < K;
+        g32_cp_async4(&xs[stage][i][kk], ok ? x + (size_t)i * ldx + k0 + kk : x, ok);
+      }
     }
     asm volatile("cp.async.commit_group;\n" ::);
   };
@@ -150,17 +169,31 @@ gemm_f32_small_kernel(const float* __restrict__ x, int ldx, const float* __restr
       asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     }
     __syncthreads();
-    const int kn = K - k0 < G32S_KT ? K - k0 : G32S_KT;
-    int c = 0;
-    for (; c + 4 <= kn; c += 4) {
-      const float4 a = *reinterpret_cast<const float4*>(&xs[stage][m][c]);
-      const float4 b = *reinterpret_cast<const float4*>(&ws[stage][nl][c]);
-      acc = fmaf(a.x, b.x, acc);
-      acc = fmaf(a.y, b.y, acc);
-      acc = fmaf(a.z, b.z, acc);
-      acc = fmaf(a.w, b.w, acc);
+    const float* xr = xs[stage][m];
+    const float* wr = ws[stage][nl];
+    if (K - k0 >= G32S_KT) {  // a full stage: a loop of known length, unrolled
+#pragma unroll 8
+      for (int c = 0; c < G32S_KT; c += 4) {
+        const float4 a = *reinterpret_cast<const float4*>(xr + c);
+        const float4 b = *reinterpret_cast<const float4*>(wr + c);
+        acc = fmaf(a.x, b.x, acc);
+        acc = fmaf(a.y, b.y, acc);
+        acc = fmaf(a.z, b.z, acc);
+        acc = fmaf(a.w, b.w, acc);
+      }
+    } else {
+      const int kn = K - k0;
+      int c = 0;
+      for (; c + 4 <= kn; c += 4) {
+        const float4 a = *reinterpret_cast<const float4*>(xr + c);
+        const float4 b = *reinterpret_cast<const float4*>(wr + c);
+        acc = fmaf(a.x, b.x, acc);
+        acc = fmaf(a.y, b.y, acc);
+        acc = fmaf(a.z, b.z, acc);
+        acc = fmaf(a.w, b.w, acc);
+      }
+      for (; c < kn; ++c) acc = fmaf(xr[c], wr[c], acc);
     }
-    for (; c < kn; ++c) acc = fmaf(xs[stage][m][c], ws[stage][nl][c], acc);
     __syncthreads();  // all are done with this stage before the copies after the next are requested into it
   }
   const int n = n0 + nl;
@@ -173,14 +206,25 @@ MS_API int ms_gemm_f32(const float* x, int ldx, const float* w, const float* bia
   if (M == 0) return 0;
   MS_REQUIRE(M > 0 && N > 0 && K > 0 && ldx >= K && ldo >= N, "gemm_f32: bad sizes M=%d N=%d K=%d ldx=%d ldo=%d", M, N, K,
              ldx, ldo);
-  if (M <= G32S_ROWS) {
-    gemm_f32_small_kernel<<<(N + G32S_COLS - 1) / G32S_COLS, G32S_ROWS * G32S_COLS, 0, stream>>>(x, ldx, w, bias, out, ldo, M, N, K);
+  const bool vec = K % 4 == 0 && ldx % 4 == 0 && ((uintptr_t)x | (uintptr_t)w) % 16 == 0;
+  if (M <= 16) {
+#define MS_G32_SMALL(ROWS, COLS)                                                                                       \
+  do {                                                                                                                 \
+    if (vec)                                                                                                           \
+      gemm_f32_small_kernel<ROWS, COLS, true><<<(N + COLS - 1) / COLS, ROWS * COLS, 0, stream>>>(x, ldx, w, bias, out, ldo, M, N, K); \
+    else                                                                                                               \
+      gemm_f32_small_kernel<ROWS, COLS, false><<<(N + COLS - 1) / COLS, ROWS * COLS, 0, stream>>>(x, ldx, w, bias, out, ldo, M, N, K); \
+  } while (0)
+    if (M <= 8)
+      MS_G32_SMALL(8, 16);
+    else
+      MS_G32_SMALL(16, 8);
+#undef MS_G32_SMALL
     MS_LAUNCH_CHECK("gemm_f32");
     return 0;
   }
   dim3 grid((N + G32_BN - 1) / G32_BN, (M + G32_BM - 1) / G32_BM);
   MS_REQUIRE(grid.y <= 65535, "gemm_f32: %d rows are more than one launch takes", M);
-  const bool vec = K % 4 == 0 && ldx % 4 == 0 && ((uintptr_t)x | (uintptr_t)w) % 16 == 0;
   if (vec)
     gemm_f32_kernel<true><<<grid, 256, 0, stream>>>(x, ldx, w, bias, out, ldo, M, N, K);
   else
