@@ -109,6 +109,11 @@ def cmd_bench(a) -> int:
 
 
 def main(argv=None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if argv[:1] == ["timeline"]:  # its options are the timeline program's own (argparse would not pass "--shape ..." on)
+        from . import timeline
+
+        return timeline.main(argv[1:])
     ap = argparse.ArgumentParser(prog="mach", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="cmd", required=True)
 
