@@ -135,8 +135,8 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
   // What the blocks of a cluster hand each other at the end: block k puts its part of (head, coordinate) pair e into
   // the shared memory of the block that merges e, at [k][e - that block's first pair], and its heads' maxima and
   // sums into every block's.  Nothing else lives here, so the others may write while this block still attends.
-  __shared__ float gath_o[16 * HD + 8];
-  __shared__ float gath_m[8][16], gath_l[8][16];
+  __shared__ __align__(16) float gath_o[16 * HD + 32];
+  __shared__ float2 gath_ml[8][16];  // (maximum, sum)
 
   MS_TIMELINE_BEGIN(200);
   ms_pdl_trigger();
@@ -384,34 +384,39 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
   __syncthreads();
   cg::cluster_group cluster = cg::this_cluster();
   const int total = groups * HD;
-  const int per_share = (total + num_splits - 1) / num_splits;  // pairs a block of the cluster merges
-  for (int e = tid; e < total; e += DCL_THREADS) {
-    const int r = e / HD, d = e - r * HD;
+  // pairs a block of the cluster merges: a multiple of four, so that four neighbours go to the same block in one store
+  // (a store into another block's shared memory costs a thread hundreds of cycles: few and wide ones)
+  const int per_share = (((total + num_splits - 1) / num_splits) + 3) & ~3;
+  for (int e = 4 * tid; e < total; e += 4 * DCL_THREADS) {
+    const int r = e / HD, d = e - r * HD;  // the pairs e .. e + 3 are coordinates d .. d + 3 of row r
     float m = -INFINITY;
 #pragma unroll
     for (int w = 0; w < DCL_WARPS; ++w) m = fmaxf(m, red_m[w * 16 + r]);
-    float o = 0.f, l = 0.f;
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    float l = 0.f;
 #pragma unroll
     for (int w = 0; w < DCL_WARPS; ++w) {
       const float mw = red_m[w * 16 + r];
       const float f = mw == -INFINITY ? 0.f : ms_exp2(mw - m);
-      o += red_o[((size_t)w * 16 + r) * HD + d] * f;
+      const float4 ow = *reinterpret_cast<const float4*>(red_o + ((size_t)w * 16 + r) * HD + d);
+      o.x += ow.x * f;
+      o.y += ow.y * f;
+      o.z += ow.z * f;
+      o.w += ow.w * f;
       l += red_l[w * 16 + r] * f;
     }
     if (num_splits == 1) {
-      if (live) out[((size_t)t * hq + kvh * groups + r) * HD + d] = __float2bfloat16_rn(l > 0.f ? __fdividef(o, l) : 0.f);
-    } else {
-      // to the block that merges this pair (stores through distributed shared memory: one way, no round trip)
-      const int owner = e / per_share;
-      cluster.map_shared_rank(gath_o, owner)[split * per_share + (e - owner * per_share)] = o;
-      if (d == 0) {
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-          if (k < num_splits) {
-            cluster.map_shared_rank(&gath_m[0][0], k)[split * 16 + r] = m;
-            cluster.map_shared_rank(&gath_l[0][0], k)[split * 16 + r] = l;
-          }
+      if (live) {
+        __nv_bfloat16* dst = out + ((size_t)t * hq + kvh * groups + r) * HD + d;
+        *reinterpret_cast<uint2*>(dst) = make_uint2(ms_pack_bf16(l > 0.f ? __fdividef(o.x, l) : 0.f, l > 0.f ? __fdividef(o.y, l) : 0.f),
+                                                    ms_pack_bf16(l > 0.f ? __fdividef(o.z, l) : 0.f, l > 0.f ? __fdividef(o.w, l) : 0.f));
       }
+    } else {
+      // to the block that merges these pairs (stores through distributed shared memory: one way, no round trip)
+      const int owner = e / per_share;
+      *reinterpret_cast<float4*>(cluster.map_shared_rank(gath_o, owner) + split * per_share + (e - owner * per_share)) = o;
+      // the row's maximum and sum go to every block: the row's threads share the blocks between them
+      for (int k = d / 4; k < num_splits; k += HD / 4) cluster.map_shared_rank(&gath_ml[0][0], k)[split * 16 + r] = make_float2(m, l);
     }
   }
   if (num_splits == 1) return;
@@ -429,8 +434,8 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
         const bool in = k < num_splits;
-        mk[k] = in ? gath_m[k][r] : -INFINITY;
-        lk[k] = in ? gath_l[k][r] : 0.f;
+        mk[k] = in ? gath_ml[k][r].x : -INFINITY;
+        lk[k] = in ? gath_ml[k][r].y : 0.f;
         ok[k] = in ? gath_o[k * per_share + (e - split * per_share)] : 0.f;
       }
       float m = -INFINITY;
