@@ -365,15 +365,16 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
     st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
     st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
   }
-  float* red_o = reinterpret_cast<float*>(kv_s);       // [DCL_WARPS][16][HD]
-  float* red_m = red_o + DCL_WARPS * 16 * HD;          // [DCL_WARPS][16]
+  constexpr int RED = HD + 8;  // (rows eight banks apart: a warp's 8-byte stores below collide two ways, not eight)
+  float* red_o = reinterpret_cast<float*>(kv_s);       // [DCL_WARPS][16][RED]
+  float* red_m = red_o + DCL_WARPS * 16 * RED;         // [DCL_WARPS][16]
   float* red_l = red_m + DCL_WARPS * 16;               // [DCL_WARPS][16]
   const int g0 = lane >> 2, c0 = 2 * (lane & 3);
 #pragma unroll
   for (int j = 0; j < HD / 8; ++j) {
-    float* base = red_o + (warp * 16 + g0) * HD + j * 8 + c0;
+    float* base = red_o + (warp * 16 + g0) * RED + j * 8 + c0;
     *reinterpret_cast<float2*>(base) = make_float2(st.o[j][0], st.o[j][1]);
-    *reinterpret_cast<float2*>(base + 8 * HD) = make_float2(st.o[j][2], st.o[j][3]);
+    *reinterpret_cast<float2*>(base + 8 * RED) = make_float2(st.o[j][2], st.o[j][3]);
   }
   if ((lane & 3) == 0) {
     red_m[warp * 16 + g0] = st.m[0];
@@ -398,7 +399,7 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
     for (int w = 0; w < DCL_WARPS; ++w) {
       const float mw = red_m[w * 16 + r];
       const float f = mw == -INFINITY ? 0.f : ms_exp2(mw - m);
-      const float4 ow = *reinterpret_cast<const float4*>(red_o + ((size_t)w * 16 + r) * HD + d);
+      const float4 ow = *reinterpret_cast<const float4*>(red_o + ((size_t)w * 16 + r) * RED + d);
       o.x += ow.x * f;
       o.y += ow.y * f;
       o.z += ow.z * f;
@@ -498,7 +499,7 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
 static size_t dcl_smem_bytes(int hd, int stages, int DCL_WARPS) {
   const size_t stride = hd + 8;
   const size_t tiles = (16 + (size_t)stages * 2 * DCL_TILE) * stride * sizeof(__nv_bfloat16);
-  const size_t red = 16 * stride * sizeof(__nv_bfloat16) + ((size_t)DCL_WARPS * 16 * (hd + 2) + 16 * hd) * sizeof(float);
+  const size_t red = 16 * stride * sizeof(__nv_bfloat16) + ((size_t)DCL_WARPS * 16 * (hd + 8 + 2) + 16 * hd) * sizeof(float);
   return tiles > red ? tiles : red;
 }
 
