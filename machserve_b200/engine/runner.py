@@ -169,7 +169,7 @@ class ModelRunner:
         # (a step of any shape that is to be replayed from a graph is padded to a multiple of ROW_BUCKET rows and of
         # SEQ_BUCKET sequences)
         rows = max(-(-max_step_tokens // self.ROW_BUCKET) * self.ROW_BUCKET, pad)
-        seqs = max(pad, max_requests + self.SEQ_BUCKET)
+        seqs = max(pad, 4 * max_requests + self.SEQ_BUCKET)
         self._stage_len = 6 * rows + 4 * seqs + 1 + sum(p.plan_words(rows, seqs) for p in self._planners.values()) + 16
         self._pinned = [torch.empty(self._stage_len, dtype=torch.int32).pin_memory() for _ in range(3)]
         self._pinned_events: List[Optional[torch.cuda.Event]] = [None] * len(self._pinned)
@@ -377,6 +377,23 @@ class ModelRunner:
 
     ROW_BUCKET, SEQ_BUCKET, WANT_BUCKET = 64, 16, 16
 
+    @classmethod
+    def padded_sizes(cls, rows: int, seqs: int, wanted: int) -> Tuple[int, int, int]:
+        """The sizes a step of any shape is padded to when it is to share a captured graph: rows to 16 (the few-row
+        kernels' limit), 32 or a multiple of ROW_BUCKET; sequences and wanted rows to SEQ_BUCKET and WANT_BUCKET times
+        a power of four (16, 64, 256, ...: what is padded there costs next to nothing, and every class less is a
+        graph less), wanted rows never to more than the rows."""
+        def coarse(n: int, unit: int) -> int:
+            c = unit
+            while c < n:
+                c *= 4
+            return c
+
+        rows_p = 16 if rows <= 16 else 32 if rows <= 32 else -(-rows // cls.ROW_BUCKET) * cls.ROW_BUCKET
+        seqs_p = coarse(seqs, cls.SEQ_BUCKET)
+        wanted_p = min(coarse(wanted, cls.WANT_BUCKET), rows_p) if wanted else 0
+        return rows_p, seqs_p, wanted_p
+
     def _stage(self, entries: Sequence[StepEntry], bucketed: bool = False) -> StepContext:
         """Fills one pinned buffer with the step's index arrays and copies it to the device in one transfer.
         `bucketed`: the step is padded to 16, 32 or a multiple of ROW_BUCKET rows by rows that belong to no sequence and
@@ -393,12 +410,8 @@ class ModelRunner:
         for n in counts:
             row0.append(row)
             row += n
-        extra = 0
-        if bucketed:  # 16 rows (the few-row kernels' limit), 32, then multiples of ROW_BUCKET
-            extra = (16 if T <= 16 else 32 if T <= 32 else -(-T // self.ROW_BUCKET) * self.ROW_BUCKET) - T
-        empty = -S % self.SEQ_BUCKET if bucketed else 0
-        Tp, Sp = T + extra, S + empty
-        Wp = min(max(self.WANT_BUCKET, 1 << (W - 1).bit_length()), Tp) if bucketed and W else W
+        Tp, Sp, Wp = self.padded_sizes(T, S, W) if bucketed else (T, S, W)
+        extra, empty = Tp - T, Sp - S
         shape = StepShape(Tp, Sp, row0 + [T] * empty, counts + [0] * empty, starts + [0] * empty, bucketed)
         plans, plan_sizes = self._plans(shape)
         views, total = self._layout(Tp, Sp, Wp, plan_sizes)

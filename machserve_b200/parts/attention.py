@@ -107,7 +107,7 @@ class Attention(Mixer):
         return self.PLAN
 
     def plan_words(self, max_rows, max_seqs):
-        return max_seqs + 2 * (max_rows // self.TILE + max_seqs + 4) + 2 * (max_rows // self.BIG_TILE + max_seqs + 2)
+        return 4 * max_seqs + 16 + 2 * (max_rows // self.TILE + max_seqs + 4) + 2 * (max_rows // self.BIG_TILE + max_seqs + 2)
 
     def plan(self, step):
         """Rows that are alone in their sequence (decoding) go to the kernel that splits a row's keys over blocks;
@@ -144,8 +144,13 @@ class Attention(Mixer):
                 pad = -len(rows0) % multiple
                 rows0 += [0] * pad
                 rows_n += [0] * pad
-            single += [-1] * (-len(single) % 16)  # (no row: the blocks of such an entry do nothing)
+            if single:  # 16, 64, 256, ... entries (-1: no row; the blocks of such an entry do nothing)
+                want = 16
+                while want < len(single):
+                    want *= 4
+                single += [-1] * (want - len(single))
             classes = [1 << (c - 1).bit_length() if c > 0 else 0 for c in classes]
+            classes[2] = 4 * classes[1]  # (the bound that the portions' class gives: 512 keys are 4 tiles)
         lists = {"single_rows": single, "tile_row0": t0, "tile_rows": tn, "big_tile_row0": b0, "big_tile_rows": bn}
         return WorkPlan(lists, tuple(classes))
 
