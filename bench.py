@@ -167,7 +167,8 @@ def free_device_memory():
 
 def time_gemm_pair_tc(torch, ops, a, pk) -> int:
     """The four products of a layer at `--prefill` rows: the repository's tcgen05 product with its fused epilogues (a
-    pair of SMs per tile; tests only, the engine multiplies with the library above 16 rows) beside the library's."""
+    pair of SMs per tile; the engine uses its gated form for the feed-forward from 1,024 rows on and the library for
+    the other products above 16 rows) beside the library's."""
     raw = SHAPES[a.shape]
     h, inter = raw["hidden_size"], raw["intermediate_size"]
     hd = raw.get("head_dim", h // raw["num_attention_heads"])
