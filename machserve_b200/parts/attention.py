@@ -271,7 +271,7 @@ class Attention(Mixer):
         if parts > 1:
             per = -(-tiles // (8 * parts))
             stages = min(per, self.max_stages)
-            warps = 8 if hd <= 64 and 8 * units * parts <= sm else 4
+            warps = 8 if hd <= 64 else 4
             self._launch_cache[key] = (splits, stages, warps, 0, parts)
             return self._launch_cache[key]
         blocks = splits * units
