@@ -106,3 +106,39 @@ def test_a_serving_load_comes_to_few_classes():
     assert len(steps) > 100
     assert len(seen) <= ModelRunner.MAX_SHAPE_GRAPHS, f"{len(seen)} classes after three loads"
     assert hits >= 0.8 * len(steps), f"only {hits} of {len(steps)} prompt-bearing steps of a new load fall into a captured class"
+
+
+def test_decode_attention_launch_rule():
+    """The launch shape of the decode attention for the cases it was measured at: (blocks a cluster, tiles held at once,
+    warps, keys a warp takes at a time, clusters a row).  Host arithmetic only; it asks the kernel library for two of
+    its constants, so it is skipped where the library cannot be built."""
+    import types
+
+    import pytest
+
+    from machserve_b200 import ops
+
+    try:
+        max_stages = {64: ops.attention_decode_cluster_max_stages(64), 128: ops.attention_decode_cluster_max_stages(128)}
+    except Exception as e:  # no compiler here
+        pytest.skip(f"the kernel library is not available: {e}")
+
+    def rule(hd, units, tiles):
+        att = Attention.__new__(Attention)
+        att.rt, att.hd, att.max_stages, att._launch_cache = types.SimpleNamespace(sm_count=148), hd, max_stages[hd], {}
+        return att._single_launch(units, tiles)
+
+    # head size 64, two kv heads: batch 8 at 2,048 keys (the benchmark's step): eight blocks a cluster, each holds its run
+    assert rule(64, 16, 40) == (8, 5, 8, 0, 1)
+    # batch 64: four blocks a cluster (512 blocks, all resident), a ring of two tiles, a quarter of a tile per warp
+    assert rule(64, 128, 40) == (4, 2, 4, 16, 1)
+    # batch 1 at 32,768 keys: eight clusters a row; at 8,192 keys: four; at 2,048: one
+    assert rule(64, 2, 520)[4] == 8 and rule(64, 2, 136)[4] == 4 and rule(64, 2, 40)[4] == 1
+    # batch 8: several clusters only from 32,768 keys on (a second block per SM delays the kernels that follow)
+    assert rule(64, 16, 264)[4] == 1 and rule(64, 16, 520)[4] == 2
+    # never more clusters than 16, never fewer than four tiles a block
+    for units in (1, 2, 4, 8, 16, 64):
+        for tiles in (8, 40, 136, 520, 2056):
+            splits, stages, warps, kpw, parts = rule(128, units, tiles)
+            assert 1 <= parts <= 16 and 1 <= stages <= max_stages[128] and warps in (4, 8)
+            assert parts == 1 or tiles // (8 * parts) >= 4
