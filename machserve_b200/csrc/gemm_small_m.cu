@@ -408,7 +408,7 @@ struct GsmPlan {
 };
 
 #define GSM_STAGE_BYTES (48 * 1024)  // most shared memory for staged weights per block: 1 KB per warp and chunk
-#define GSM_XS_BYTES (32 * 1024)     // most shared memory for the activations per block
+#define GSM_XS_BYTES (48 * 1024)     // most shared memory for the activations per block (16 rows of a block's share of K = 4,864 in a cluster of four: 41.5 KB)
 
 // 8 warps a block and about three blocks per SM, the k range split over a cluster when there are few blocks of
 // rows.  When that would leave a short second wave of blocks (which would start their copies only after the
