@@ -529,6 +529,25 @@ MS_TIMELINE_SETTER(ms_timeline_set_gemm_small_m)
 
 MS_API int ms_gemm_small_m_supports(int M, int N, int K) { return M >= 1 && M <= 64 && N >= 1 && K >= 8 && K % 8 == 0; }
 
+// How a product of M rows with N outputs over K would be spread (host arithmetic only, for tests and notes).
+// gated: the gate/up form (N = the intermediate size), else a product with 16 weight rows a block; residual: the
+// residual-adding form.  plan: {warps, blocks of rows a thread block, blocks a cluster, chunks a warp stages in
+// shared memory, chunks it holds in registers, row stride of the staged activations (0: read from global memory after
+// the wait), dynamic shared memory in bytes}.
+MS_API int ms_gemm_small_m_plan(int M, int N, int K, int gated, int residual, int sm_count, int* plan) {
+  MS_REQUIRE(ms_gemm_small_m_supports(M, N, K) && plan != nullptr, "gemm_small_m_plan: M=%d (1..64), N=%d, K=%d (a multiple of 8) is not covered", M, N, K);
+  const int blocks = gated ? (N + 7) / 8 : (N + 15) / 16;
+  const GsmPlan p = gsm_plan(blocks, M, K, gated ? GSM_EPI_SILU_MUL : residual ? GSM_EPI_RESADD : GSM_EPI_BF16, sm_count);
+  plan[0] = p.warps;
+  plan[1] = p.rb;
+  plan[2] = p.sh.cluster_size;
+  plan[3] = p.sh.staged;
+  plan[4] = p.sh.held;
+  plan[5] = p.sh.xs_stride;
+  plan[6] = (int)p.smem;
+  return 0;
+}
+
 // out[M, N] = x[M, K] . w[N, K]^T.  x, w bfloat16; out bfloat16 (out_dtype MS_BF16) or float32.
 MS_API int ms_gemm_small_m(const void* x, int ldx, const void* w, void* out, int out_dtype, int ldo, int M, int N,
                            int K, int sm_count, cudaStream_t stream) {

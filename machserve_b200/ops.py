@@ -73,6 +73,7 @@ class _Signatures:
     ms_attention_generic = [P, P, P, P, I, I, P, P, P, I, I, I, I, I, I, I, I, F, I, P]
     ms_gemm_f32 = [P, I, P, P, P, I, I, I, I, P]
     ms_attention_decode = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P]
+    ms_gemm_small_m_plan = [I, I, I, I, I, I, P]
     ms_attention_decode_cluster = [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, I, I, I, P, LL, P, I, P]
     ms_attention_decode_cluster_rope = [P, I, P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, I, I, I, P, LL, P, I, P]
     ms_attention_prefill_tc = [P, P, P, P, I, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, LL, P, LL, P]
@@ -537,6 +538,16 @@ def gemm_small_m_silu_mul(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Ten
         "gemm_small_m_silu_mul",
     )
     return out
+
+
+def gemm_small_m_plan(m: int, n: int, k: int, gated: bool = False, residual: bool = False, sms: Optional[int] = None) -> dict:
+    """How the few-row product of m rows with n outputs over k is spread over a GPU of `sms` SMs (this one's by default):
+    host arithmetic only."""
+    plan = (c_int * 7)()
+    _check(lib().ms_gemm_small_m_plan(int(m), int(n), int(k), 1 if gated else 0, 1 if residual else 0,
+                                      int(sms) if sms else sm_count(), plan), "gemm_small_m_plan")
+    names = ("warps", "row_blocks", "cluster", "staged_chunks", "held_chunks", "activation_stride", "shared_bytes")
+    return dict(zip(names, (int(v) for v in plan)))
 
 
 def gemm_small_m_stats_blocks(n: int) -> int:

@@ -142,3 +142,29 @@ def test_decode_attention_launch_rule():
             splits, stages, warps, kpw, parts = rule(128, units, tiles)
             assert 1 <= parts <= 16 and 1 <= stages <= max_stages[128] and warps in (4, 8)
             assert parts == 1 or tiles // (8 * parts) >= 4
+
+
+def test_few_row_products_stage_their_activations():
+    """The few-row products bring their share of the activation rows into shared memory before they multiply; when the
+    share does not fit they read it from global memory chunk by chunk after their wait, which costs a decoding step of 9
+    to 16 rows at 0.5B sizes about a tenth of its time.  At those sizes every product of up to 16 rows stages them, at
+    1.5B sizes every product of up to 8 rows (with more rows, and at larger sizes, the gate/up and down products' shares
+    outgrow the 48 KB set aside).  Host arithmetic of the kernel library; skipped where the library cannot be built."""
+    import pytest
+
+    from machserve_b200 import ops
+
+    try:
+        ops.gemm_small_m_plan(8, 896, 896, sms=148)
+    except Exception as e:  # no compiler here
+        pytest.skip(f"the kernel library is not available: {e}")
+    for name, (hidden, qkv, inter), most in (("0.5b", (896, 1152, 4864), (1, 8, 9, 16)), ("1.5b", (1536, 2048, 8960), (1, 8))):
+        for rows in most:
+            for what, plan in (("qkv", ops.gemm_small_m_plan(rows, qkv, hidden, sms=148)),
+                               ("output", ops.gemm_small_m_plan(rows, hidden, hidden, residual=True, sms=148)),
+                               ("gate/up", ops.gemm_small_m_plan(rows, inter, hidden, gated=True, sms=148)),
+                               ("down", ops.gemm_small_m_plan(rows, hidden, inter, residual=True, sms=148))):
+                assert plan["activation_stride"] > 0, f"{name} {what} at {rows} rows reads its activations from global memory: {plan}"
+                assert plan["shared_bytes"] <= 96 * 1024 and plan["cluster"] in (1, 2, 4)
+    # what does not fit is read after the wait (the kernel's other path), never staged in part
+    assert ops.gemm_small_m_plan(16, 1536, 8960, residual=True, sms=148)["activation_stride"] == 0
