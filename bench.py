@@ -30,7 +30,10 @@ This engine runs on one GPU: for --gpus > 1 it says so and exits with 2.
 
     python bench.py --kernel attention_prefill
 
-times the prompt attention kernel alone (2,048, 4,096 and 8,192 tokens) and prints a line of its own.
+times the prompt attention kernel alone (2,048, 4,096 and 8,192 tokens) and prints a line of its own;
+`--kernel gemm [--shape ...] [--prefill ROWS]` the four products of a layer with their fused epilogues beside the
+library's.  `--profile decode|prefill|mixed` brackets that timed region with cudaProfilerStart/Stop, for a profiler
+started with --profile-from-start off (the commands are in profiles/).
 """
 from __future__ import annotations
 
